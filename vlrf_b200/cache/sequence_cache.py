@@ -4,11 +4,14 @@ A sequence holds one *slot* from its first step to its end.  What a layer keeps 
 by its mixer as a *need*:
 
   KVNeed     keys and values per token: all of them (kind "full") or the last `window` (kind "window")
+  LatentNeed one row of `width` numbers per token (a latent from which a mixer derives every head's keys and
+             values, with whatever else it keeps per token in the same row): all of them, or the last `window`
   StateNeed  a state of fixed size per sequence (for mixers that carry one)
 
 Layers with equal needs form a *group* with storage of its own.  A key/value group owns a pool of
 blocks of `block_tokens` tokens, K and V of shape [layer in group, block, kv_head, block_tokens,
-head_dim], and a table [slot, block index] → block; blocks are taken as a sequence grows and go back
+head_dim] (a latent group: rows of shape [layer in group, block, block_tokens, width]), and a table
+[slot, block index] → block; blocks are taken as a sequence grows and go back
 to the pool when it ends (for a window group, also once they lie wholly before the window).  A state
 group owns [layer in group, slot, *shape], zeroed when a slot is taken.  `max_tokens` sizes every
 key/value pool: it is the most tokens that live sequences hold at one time, each sequence's count
@@ -39,6 +42,13 @@ class KVNeed:
 
 
 @dataclasses.dataclass(frozen=True)
+class LatentNeed:
+    width: int              # numbers kept per token
+    kind: str = "full"      # "full" | "window"
+    window: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
 class StateNeed:
     shape: tuple
     dtype: torch.dtype = torch.float32
@@ -52,15 +62,21 @@ class CacheView:
     v: torch.Tensor | None = None
     block_table: torch.Tensor | None = None  # device int32 [slot, block index]
     state: torch.Tensor | None = None        # [slot, *shape]
+    rows: torch.Tensor | None = None         # a latent group's [block, block_tokens, width]
 
 
 class _KVGroup:
     def __init__(self, need: KVNeed, entries, n_blocks, n_slots, max_blocks, dtype, device):
         self.need, self.entries = need, list(entries)
         self.pool = FreeList(n_blocks, "cache block")
-        shape = (len(self.entries), n_blocks, need.n_kv_heads, BLOCK_TOKENS, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        if isinstance(need, LatentNeed):
+            self.k = self.v = None
+            self.rows = torch.zeros((len(self.entries), n_blocks, BLOCK_TOKENS, need.width), dtype=dtype, device=device)
+        else:
+            shape = (len(self.entries), n_blocks, need.n_kv_heads, BLOCK_TOKENS, need.head_dim)
+            self.k = torch.zeros(shape, dtype=dtype, device=device)
+            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.rows = None
         # the host's copy of the table lies in pinned memory where there is a GPU, so that bringing the device's
         # copy up to date is an asynchronous copy; `before_write` waits for a copy still reading it
         self._pinned = None
@@ -137,9 +153,11 @@ class SequenceCache:
                 continue
             by_need.setdefault(need, []).append(entry)
         for need, entries in by_need.items():
-            if isinstance(need, KVNeed):
+            if isinstance(need, (KVNeed, LatentNeed)):
                 if need.kind not in ("full", "window"):
                     raise CacheError(f"unknown key/value need kind '{need.kind}'")
+                if isinstance(need, LatentNeed) and need.width <= 0:
+                    raise CacheError("a latent need keeps at least one number per token")
                 if need.kind == "window" and need.window <= 0:
                     raise CacheError("a window need has a positive window")
                 g = _KVGroup(need, entries, self.n_blocks, self.n_slots, self.max_blocks, dtype, self.device)
@@ -157,13 +175,17 @@ class SequenceCache:
             raise CacheError(f"cache entry {entry} keeps nothing")
         g, i = self._where[entry]
         if isinstance(g, _KVGroup):
+            if g.rows is not None:
+                return CacheView(g.need, rows=g.rows[i], block_table=g.table_dev)
             return CacheView(g.need, k=g.k[i], v=g.v[i], block_table=g.table_dev)
         return CacheView(g.need, state=g.state[i])
 
     def bytes(self) -> int:
         total = 0
         for g in self._groups:
-            if isinstance(g, _KVGroup):
+            if isinstance(g, _KVGroup) and g.rows is not None:
+                total += g.rows.numel() * g.rows.element_size()
+            elif isinstance(g, _KVGroup):
                 total += 2 * g.k.numel() * g.k.element_size()
             else:
                 total += g.state.numel() * g.state.element_size()
@@ -174,7 +196,10 @@ class SequenceCache:
         total = 0
         for g in self._groups:
             if isinstance(g, _KVGroup):
-                per_tok = 2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * g.k.element_size()
+                if g.rows is not None:
+                    per_tok = len(g.entries) * g.need.width * g.rows.element_size()
+                else:
+                    per_tok = 2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * g.k.element_size()
                 for s in slots:
                     n = self.lengths[s]
                     if g.need.kind == "window":

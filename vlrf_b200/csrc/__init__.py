@@ -85,6 +85,27 @@ _SIGNATURES = {
                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_decode_program_run": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "vlrf_group_rmsnorm": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_float, _c_int, _c_void_p],
+    "vlrf_cast_rows": [_c_void_p, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
+    "vlrf_gate_mul": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_gemm_heads": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                        _c_int, _c_int, _c_void_p],
+    "vlrf_gemm_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_void_p],
+    "vlrf_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_void_p, _c_int,
+                           _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_latent_q_rows": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_attn_latent": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
+                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
+    "vlrf_moe_route": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_void_p, _c_int, _c_void_p],
+    "vlrf_moe_plan": [_c_void_p, _c_void_p, _c_int, _c_void_p],
+    "vlrf_moe_gather": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                        _c_void_p],
+    "vlrf_moe_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                         _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,

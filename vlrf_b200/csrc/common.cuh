@@ -161,9 +161,14 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 __device__ __forceinline__ float gelu_erf_f(float x) {
     return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
 }
+// relu(x)^2, x·sigmoid(x) and sigmoid(x), in float32
+__device__ __forceinline__ float relu2_f(float x) { const float r = fmaxf(x, 0.f); return r * r; }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 template <int ACT> __device__ __forceinline__ float apply_act(float x) {
     if (ACT == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
     if (ACT == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    if (ACT == VLRF_ACT_RELU2) return relu2_f(x);
     return x;
 }
 // The tanh form for results that are rounded to bfloat16 anyway: tanh in one instruction (`tanh.approx.f32`,
@@ -178,6 +183,7 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
 template <typename OT> __device__ __forceinline__ float apply_act_out(float x, int act) {
     if (act == VLRF_ACT_GELU_TANH) return sizeof(OT) == 2 ? gelu_tanh_fast(x) : gelu_tanh_f(x);
     if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    if (act == VLRF_ACT_RELU2) return relu2_f(x);
     return x;
 }
 // 32 bytes a thread in one instruction (sm_100): a thread that writes its own row piece by piece fills a whole
@@ -195,10 +201,12 @@ __device__ __forceinline__ void ld_global_32B(const void* p, float (&v)[8]) {
 template <typename OT, int ACT> __device__ __forceinline__ float apply_act_const(float x) {
     if (ACT == VLRF_ACT_GELU_TANH) return sizeof(OT) == 2 ? gelu_tanh_fast(x) : gelu_tanh_f(x);
     if (ACT == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    if (ACT == VLRF_ACT_RELU2) return relu2_f(x);
     return x;
 }
 __device__ __forceinline__ float apply_act_rt(float x, int act) {
     if (act == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
     if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    if (act == VLRF_ACT_RELU2) return relu2_f(x);
     return x;
 }

@@ -75,7 +75,7 @@ extern "C" int vlrf_gemm_simt(const void* X, const void* W, const float* bias, c
                               int act, cudaStream_t stream) {
     VLRF_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     VLRF_REQUIRE(ldx >= K && ldy >= N, "gemm: leading sizes ldx=%d ldy=%d are smaller than K=%d N=%d", ldx, ldy, K, N);
-    VLRF_REQUIRE(act >= 0 && act <= 2, "gemm: unknown activation %d", act);
+    VLRF_REQUIRE(act >= 0 && act <= VLRF_ACT_LAST_FUSED, "gemm: unknown activation %d", act);
     if (M == 0) return VLRF_OK;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     VLRF_REQUIRE(grid.y <= 65535, "gemm: M=%d needs more than 65535 row tiles", M);

@@ -418,7 +418,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     VLRF_REQUIRE(M >= 1 && M <= 64, "gemm_skinny: takes 1…64 rows, not %d", M);
     VLRF_REQUIRE(N > 0 && K > 0 && K % 32 == 0, "gemm_skinny: K=%d must be a positive multiple of 32", K);
     VLRF_REQUIRE(ldx >= K && ldy >= N, "gemm_skinny: leading sizes too small");
-    VLRF_REQUIRE(act >= 0 && act <= 2, "gemm_skinny: unknown activation %d", act);
+    VLRF_REQUIRE(act >= 0 && act <= VLRF_ACT_LAST_FUSED, "gemm_skinny: unknown activation %d", act);
     VLRF_REQUIRE(x_is_f32_ln || ldx % 8 == 0, "gemm_skinny: bf16 rows must start on 16-byte boundaries (ldx=%d)", ldx);
     
     VLRF_REQUIRE(dev_err != nullptr, "gemm_skinny: needs the device error word");

@@ -712,7 +712,7 @@ extern "C" int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, c
                                 // the same for the rows of Y, [M][ceil(N/32)][2], for a later product to use
                                 const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_gemm_splitk_takes(M, N, K, ldx, x_is_f32_ln), "gemm_splitk: does not take M=%d N=%d K=%d ldx=%d", M, N, K, ldx);
-    VLRF_REQUIRE(ldx >= K && ldy >= N && act >= 0 && act <= 2, "gemm_splitk: bad arguments");
+    VLRF_REQUIRE(ldx >= K && ldy >= N && act >= 0 && act <= VLRF_ACT_LAST_FUSED, "gemm_splitk: bad arguments");
     VLRF_REQUIRE(dev_err != nullptr, "gemm_splitk: needs the device error word");
     VLRF_REQUIRE(!x_is_f32_ln || (gamma && beta && stats_in), "gemm_splitk: the fused LayerNorm needs weight, bias and the rows' statistics");
     VLRF_REQUIRE(stats_out == nullptr || ((N + 31) / 32 <= SP_STAT_SEGS && out_dtype == VLRF_F32),

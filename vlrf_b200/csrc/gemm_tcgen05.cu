@@ -239,6 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             };
                             if (act == VLRF_ACT_NONE) rows(std::integral_constant<int, VLRF_ACT_NONE>{});
                             else if (act == VLRF_ACT_GELU_TANH) rows(std::integral_constant<int, VLRF_ACT_GELU_TANH>{});
+                            else if (act == VLRF_ACT_RELU2) rows(std::integral_constant<int, VLRF_ACT_RELU2>{});
                             else rows(std::integral_constant<int, VLRF_ACT_GELU_ERF>{});
                         }
                     }
@@ -358,6 +359,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     };
                     if (act == VLRF_ACT_NONE) fast_body(std::integral_constant<int, VLRF_ACT_NONE>{});
                     else if (act == VLRF_ACT_GELU_TANH) fast_body(std::integral_constant<int, VLRF_ACT_GELU_TANH>{});
+                    else if (act == VLRF_ACT_RELU2) fast_body(std::integral_constant<int, VLRF_ACT_RELU2>{});
                     else fast_body(std::integral_constant<int, VLRF_ACT_GELU_ERF>{});
                 } else {
                     const float* rrow = residual ? residual + (size_t)m * ldy + n0 + c0 : nullptr;
@@ -442,7 +444,7 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
                                  const int* tok_pos, int k_off, int v_off, int Hkv, int dh, int BT, int* dev_err,
                                  cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_gemm_tcgen05_takes(M, N, K, ldx), "gemm_tcgen05: M=%d N=%d K=%d ldx=%d: K and the row stride must be multiples of 8", M, N, K, ldx);
-    VLRF_REQUIRE(ldy >= N && act >= 0 && act <= 2 && dev_err != nullptr, "gemm_tcgen05: bad arguments");
+    VLRF_REQUIRE(ldy >= N && act >= 0 && act <= VLRF_ACT_LAST_FUSED && dev_err != nullptr, "gemm_tcgen05: bad arguments");
     VLRF_REQUIRE((M + TC_BM - 1) / TC_BM <= 65535, "gemm_tcgen05: too many row tiles");
     TcKvScatter kv{};
     if (Kc != nullptr) {

@@ -1,0 +1,110 @@
+// RMS norm in groups, and the small row-wise kernels around it.
+//
+// group_rmsnorm: a row of d columns is cut into `groups` equal consecutive parts; each part is divided by
+// sqrt(mean(part²) + eps) of its own, and the whole row is multiplied by a weight vector.  groups = 1 is the plain
+// RMS norm.  The input rows are float32 (a product's float32 result, or the residual stream); sums and the division
+// are float32.  The result either replaces the output row (any dtype) or is added to it (float32: the residual
+// stream, for blocks that norm a sublayer's output before the sum).  `rows` gathers input rows (the rows whose
+// logits are wanted).  The output may be the input: a thread rewrites only elements it has read itself.
+//
+// cast_rows: float32 rows to the activation dtype (what a sublayer reads of the float32 residual stream).
+// gate_mul: out = act(a) · b element by element (act: x·sigmoid(x) for gated feed-forwards, sigmoid(x) for gates on
+// an attention's merged heads), float32 arithmetic.
+#include "common.cuh"
+
+namespace {
+constexpr int NORM_THREADS = 128;
+constexpr int NORM_MAX_GROUPS = 256;
+
+template <typename OT, bool ACC>
+__global__ void __launch_bounds__(NORM_THREADS)
+group_rmsnorm_kernel(const float* y, int ld_y, const int* __restrict__ rows, const float* __restrict__ w, OT* out,
+                     int ld_out, int d, int groups, float eps) {
+    __shared__ float inv_sm[NORM_MAX_GROUPS];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float* yr = y + (size_t)src * ld_y;
+    const int gs = d / groups;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = warp; g < groups; g += NORM_THREADS / 32) {
+        float s = 0.f;
+        for (int i = lane; i < gs; i += 32) { const float v = yr[g * gs + i]; s = fmaf(v, v, s); }
+        s = warp_sum(s);
+        if (lane == 0) inv_sm[g] = 1.f / sqrtf(s / (float)gs + eps);
+    }
+    __syncthreads();
+    OT* o = out + (size_t)r * ld_out;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+        float v = yr[i] * inv_sm[i / gs] * w[i];
+        if (ACC) v += ElemIO<OT>::load(o + i);
+        ElemIO<OT>::store(o + i, v);
+    }
+}
+
+template <typename OT>
+__global__ void cast_rows_kernel(const float* __restrict__ x, OT* __restrict__ out, long long n) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        ElemIO<OT>::store(out + i, v.x); ElemIO<OT>::store(out + i + 1, v.y);
+        ElemIO<OT>::store(out + i + 2, v.z); ElemIO<OT>::store(out + i + 3, v.w);
+    } else {
+        for (long long j = i; j < n; ++j) ElemIO<OT>::store(out + j, x[j]);
+    }
+}
+
+template <typename ET>
+__global__ void gate_mul_kernel(const ET* a, int lda, const ET* b, int ldb, ET* out, int ldo, int rows, int cols, int act) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols) return;
+    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+    const float g = ElemIO<ET>::load(a + (size_t)r * lda + c);
+    const float v = ElemIO<ET>::load(b + (size_t)r * ldb + c);
+    const float f = act == VLRF_ACT_SILU ? silu_f(g) : sigmoid_f(g);
+    ElemIO<ET>::store(out + (size_t)r * ldo + c, f * v);
+}
+}  // namespace
+
+extern "C" int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w, void* out, int out_dtype,
+                                  int ld_out, int n_rows, int d, int groups, float eps, int accumulate,
+                                  cudaStream_t stream) {
+    VLRF_REQUIRE(n_rows >= 0 && d > 0 && groups > 0 && groups <= NORM_MAX_GROUPS, "group_rmsnorm: bad sizes rows=%d d=%d groups=%d", n_rows, d, groups);
+    VLRF_REQUIRE(d % groups == 0, "group_rmsnorm: %d columns cannot be cut into %d equal parts", d, groups);
+    VLRF_REQUIRE(ld_y >= d && ld_out >= d, "group_rmsnorm: leading sizes are smaller than the row");
+    VLRF_REQUIRE(!accumulate || out_dtype == VLRF_F32, "group_rmsnorm: only float32 rows can be added to");
+    if (n_rows == 0) return VLRF_OK;
+    if (out_dtype == VLRF_F32) {
+        if (accumulate) group_rmsnorm_kernel<float, true><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps);
+        else group_rmsnorm_kernel<float, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps);
+    } else if (out_dtype == VLRF_BF16) {
+        group_rmsnorm_kernel<__nv_bfloat16, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (__nv_bfloat16*)out, ld_out, d, groups, eps);
+    } else {
+        return vlrf_fail(VLRF_ERR_INVALID_ARG, "group_rmsnorm: unknown output dtype %d", out_dtype);
+    }
+    return vlrf_check_launch("group_rmsnorm");
+}
+
+extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    VLRF_REQUIRE(n >= 0, "cast_rows: negative size");
+    if (n == 0) return VLRF_OK;
+    const unsigned blocks = (unsigned)((n + 4 * 256 - 1) / (4 * 256));
+    if (out_dtype == VLRF_BF16) cast_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, n);
+    else if (out_dtype == VLRF_F32) cast_rows_kernel<float><<<blocks, 256, 0, stream>>>(x, (float*)out, n);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "cast_rows: unknown output dtype %d", out_dtype);
+    return vlrf_check_launch("cast_rows");
+}
+
+extern "C" int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int dtype, int rows,
+                             int cols, int act, cudaStream_t stream) {
+    VLRF_REQUIRE(rows >= 0 && cols > 0 && lda >= cols && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
+    VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID, "gate_mul: the gate is x*sigmoid(x) or sigmoid(x), not %d", act);
+    if (rows == 0) return VLRF_OK;
+    const long long n = (long long)rows * cols;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == VLRF_BF16)
+        gate_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, rows, cols, act);
+    else if (dtype == VLRF_F32)
+        gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, rows, cols, act);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul: unknown dtype %d", dtype);
+    return vlrf_check_launch("gate_mul");
+}

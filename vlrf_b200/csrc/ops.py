@@ -13,7 +13,9 @@ import torch
 from . import KernelError, call
 
 F32, BF16 = 0, 1
-ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_erf": 2}
+ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3}
+#: gates of `gate_mul` (not taken by the products' epilogues)
+GATE = {"silu": 4, "sigmoid": 5}
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -538,3 +540,163 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
     call("vlrf_attn_prefill", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
          block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens, n_seqs,
          max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
+
+
+# ---- RMS norm in groups, casts, gates ------------------------------------------------------------------------------
+
+def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate: bool = False, n_rows: int | None = None) -> None:
+    """out[r] (+)= y[rows[r] if rows is given else r] normed in `groups` equal consecutive parts (each divided by
+    sqrt(mean(part²) + eps)) and multiplied by weight.  y float32; out float32 or bfloat16 (adding: float32 only).
+    out may be y itself."""
+    _dev(y, "y", torch.float32); _dev(weight, "weight", torch.float32); _dev(out, "out")
+    d = y.shape[1]
+    n = y.shape[0] if n_rows is None else n_rows
+    if rows is not None:
+        _dev(rows, "rows", torch.int32)
+        n = rows.shape[0]
+    if weight.shape[0] != d or out.shape[1] != d or out.shape[0] < n:
+        raise KernelError("group_rmsnorm: sizes do not match")
+    call("vlrf_group_rmsnorm", _ptr(y), d, _ptr(rows), _ptr(weight), _ptr(out), dtype_code(out.dtype), d, n, d, int(groups),
+         float(eps), 1 if accumulate else 0, _stream())
+
+
+def cast_rows(x, out, n_rows: int) -> None:
+    """The first n_rows float32 rows of x in out's dtype."""
+    _dev(x, "x", torch.float32); _dev(out, "out")
+    if out.shape[1] != x.shape[1] or min(out.shape[0], x.shape[0]) < n_rows:
+        raise KernelError("cast_rows: sizes do not match")
+    call("vlrf_cast_rows", _ptr(x), _ptr(out), dtype_code(out.dtype), n_rows * x.shape[1], _stream())
+
+
+def gate_mul(a, b, out, gate: str, n_rows: int, cols: int) -> None:
+    """out[r, :cols] = gate(a[r, :cols]) · b[r, :cols]; gate "silu" or "sigmoid".  a, b and out may be column ranges
+    of wider rows (views whose last stride is 1), and out may be a or b."""
+    for name, t in (("a", a), ("b", b), ("out", out)):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != out.dtype or t.shape[0] < n_rows or t.shape[1] < cols:
+            raise KernelError(f"gate_mul: {name} does not match")
+    call("vlrf_gate_mul", _ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(out), out.stride(0), dtype_code(out.dtype),
+         n_rows, cols, GATE[gate], _stream())
+
+
+# ---- products per head and per group ---------------------------------------------------------------------------------
+
+def linear_heads(x, w, out, n_rows: int) -> None:
+    """out[m, h, :] = x[m, h, :] · w[h]ᵀ for every head.  x [M, H, K] and out [M, H, N] may be views into wider rows
+    (strides (row, head, 1)); w [H, N, K] contiguous and of x's dtype; out float32 or x's dtype."""
+    _dev(w, "w", x.dtype)
+    H, N, K = w.shape
+    for name, t, last in (("x", x, K), ("out", out, N)):
+        if not t.is_cuda or t.dim() != 3 or t.stride(2) != 1 or t.shape[1] != H or t.shape[2] != last or t.shape[0] < n_rows:
+            raise KernelError(f"linear_heads: {name} {list(t.shape)} does not match w {list(w.shape)}")
+    if out.dtype not in (torch.float32, x.dtype):
+        raise KernelError("linear_heads: the result is float32 or of the operands' dtype")
+    call("vlrf_gemm_heads", _ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1), n_rows, N, K,
+         H, dtype_code(x.dtype), dtype_code(out.dtype), _stream())
+
+
+def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
+    """Rows offsets[g] … offsets[g+1]−1 of x [P, K] times w[g]ᵀ (w [G, N, K]) into the same rows of out [P, N];
+    offsets: int32 [G + 1] on the device."""
+    _dev(x, "x"); _dev(w, "w", x.dtype); _dev(out, "out"); _dev(offsets, "offsets", torch.int32)
+    G, N, K = w.shape
+    if x.shape[1] != K or out.shape[1] != N or min(x.shape[0], out.shape[0]) < n_rows or offsets.numel() < G + 1:
+        raise KernelError("linear_grouped: sizes do not match")
+    call("vlrf_gemm_grouped", _ptr(x), _ptr(w), _ptr(out), _ptr(offsets), G, n_rows, N, K, dtype_code(x.dtype),
+         dtype_code(out.dtype), _stream())
+
+
+# ---- attention over a cache of latents --------------------------------------------------------------------------------
+
+def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_dims: int, cache, block_table, tok_slot,
+                  tok_pos, n_tokens: int, dev_err) -> None:
+    """Each token's row [RMSnorm(proj[:C]) · weight | rotate(proj[C:C+R])] into the paged cache [block, BT, row]."""
+    _dev(proj, "proj", torch.float32); _dev(norm_weight, "norm_weight", torch.float32); _dev(cache, "cache")
+    _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
+    _dev(tok_pos, "tok_pos", torch.int32); _dev(dev_err, "dev_err", torch.int32)
+    if inv_freq is not None:
+        _dev(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.shape[0] < rot_dims // 2:
+            raise KernelError("latent_append: the table of frequencies is too short")
+    if proj.shape[1] < C + R or cache.shape[2] < C + R or norm_weight.shape[0] != C or proj.shape[0] < n_tokens:
+        raise KernelError("latent_append: sizes do not match")
+    call("vlrf_latent_append", _ptr(proj), proj.shape[1], C, R, _ptr(norm_weight), float(eps), _ptr(inv_freq), int(rot_dims),
+         _ptr(cache), dtype_code(cache.dtype), cache.shape[2], _ptr(block_table), block_table.shape[1], _ptr(tok_slot),
+         _ptr(tok_pos), n_tokens, cache.shape[1], _ptr(dev_err), _stream())
+
+
+def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, tok_pos, qn, qp, C: int, n_tokens: int) -> None:
+    """q float32 [T, H·(dim + R)] → qn [T, H·dim] (unrotated parts) and the last R columns of each head's C + R columns
+    of qp (rotated parts, rotated by position)."""
+    _dev(q, "q", torch.float32); _dev(qn, "qn"); _dev(qp, "qp", qn.dtype); _dev(tok_pos, "tok_pos", torch.int32)
+    if inv_freq is not None:
+        _dev(inv_freq, "inv_freq", torch.float32)
+    if q.shape[1] != n_heads * (dim + R) or qn.shape[1] != n_heads * dim or qp.shape[1] != n_heads * (C + R):
+        raise KernelError("latent_q_rows: sizes do not match")
+    call("vlrf_latent_q_rows", _ptr(q), q.shape[1], n_heads, dim, R, _ptr(inv_freq), int(rot_dims), _ptr(tok_pos), _ptr(qn),
+         qn.shape[1], _ptr(qp), qp.shape[1], C, dtype_code(qn.dtype), n_tokens, _stream())
+
+
+#: the widest latent that the attention kernels over a latent cache hold
+LATENT_MAX_RANK = 1024
+
+
+def attention_latent_kind(dtype: torch.dtype, C: int, R: int) -> dict:
+    """Which kernels attention over a latent cache of these sizes runs on."""
+    return {"prompt": "CUDA cores", "decode": "CUDA cores"}
+
+
+def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, scale: float,
+                     window: int, dev_err, ctx=None) -> None:
+    """Each token's heads (queries in latent space, [T, H·(C + R)]) attend the rows 0…position of the token's slot in
+    the latent cache [block, BT, row]; out [T, H·C] receives Σ_j p_j c_j per head."""
+    _dev(qp, "qp"); _dev(cache, "cache", qp.dtype); _dev(out, "out", qp.dtype)
+    _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
+    _dev(tok_pos, "tok_pos", torch.int32); _dev(dev_err, "dev_err", torch.int32)
+    if qp.shape[1] != n_heads * (C + R) or out.shape[1] != n_heads * C or cache.shape[2] < C + R \
+            or min(qp.shape[0], out.shape[0]) < n_tokens:
+        raise KernelError("attention_latent: sizes do not match")
+    call("vlrf_attn_latent", _ptr(qp), dtype_code(qp.dtype), qp.shape[1], _ptr(cache), cache.shape[2], C, R, _ptr(block_table),
+         block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_tokens, n_heads, cache.shape[1],
+         float(scale), int(window), _ptr(dev_err), _stream())
+
+
+# ---- routed experts --------------------------------------------------------------------------------------------------
+
+def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts, rank, gate, counts, n_tokens: int) -> None:
+    """From float32 router logits z [T, ≥ E (+1)]: ids, wts, rank [T, top], gate [T] (see the kernel library's header)."""
+    _dev(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
+    _dev(rank, "rank", torch.int32); _dev(counts, "counts", torch.int32)
+    if gate is not None:
+        _dev(gate, "gate", torch.float32)
+    if tok_slot is not None:
+        _dev(tok_slot, "tok_slot", torch.int32)
+    if z.shape[0] < n_tokens or ids.numel() < n_tokens * top or counts.numel() < n_experts:
+        raise KernelError("moe_route: sizes do not match")
+    call("vlrf_moe_route", _ptr(z), z.shape[1], n_experts, top, 1 if shared_gate else 0, _ptr(tok_slot), _ptr(ids), _ptr(wts),
+         _ptr(rank), _ptr(gate), _ptr(counts), n_tokens, _stream())
+
+
+def moe_plan(counts, offsets, n_experts: int) -> None:
+    _dev(counts, "counts", torch.int32); _dev(offsets, "offsets", torch.int32)
+    if counts.numel() < n_experts or offsets.numel() < n_experts + 1:
+        raise KernelError("moe_plan: sizes do not match")
+    call("vlrf_moe_plan", _ptr(counts), _ptr(offsets), n_experts, _stream())
+
+
+def moe_gather(h, ids, rank, offsets, sorted_rows, row_of, n_tokens: int, top: int) -> None:
+    _dev(h, "h"); _dev(sorted_rows, "sorted_rows", h.dtype); _dev(row_of, "row_of", torch.int32)
+    if sorted_rows.shape[1] != h.shape[1] or sorted_rows.shape[0] < n_tokens * top or h.shape[0] < n_tokens:
+        raise KernelError("moe_gather: sizes do not match")
+    call("vlrf_moe_gather", _ptr(h), dtype_code(h.dtype), h.shape[1], _ptr(ids), _ptr(rank), _ptr(offsets), _ptr(sorted_rows),
+         _ptr(row_of), n_tokens, top, _stream())
+
+
+def moe_combine(expert_out, row_of, wts, top: int, shared_out, gate, y, n_tokens: int, residual=None) -> None:
+    """y[t] = Σ_j wts[t, j] · expert_out[row_of[t, j]] (+ gate[t] · shared_out[t]) (+ residual[t]), float32."""
+    _dev(expert_out, "expert_out", torch.float32); _dev(y, "y", torch.float32)
+    if shared_out is not None:
+        _dev(shared_out, "shared_out", torch.float32)
+    if y.shape[1] != expert_out.shape[1] or y.shape[0] < n_tokens:
+        raise KernelError("moe_combine: sizes do not match")
+    call("vlrf_moe_combine", _ptr(expert_out), expert_out.shape[1], _ptr(row_of), _ptr(wts), top, _ptr(shared_out), _ptr(gate),
+         _ptr(residual), _ptr(y), n_tokens, _stream())

@@ -35,6 +35,10 @@ extern "C" {
 #define VLRF_ACT_NONE 0
 #define VLRF_ACT_GELU_TANH 1
 #define VLRF_ACT_GELU_ERF 2
+#define VLRF_ACT_RELU2 3          // relu(x)^2
+#define VLRF_ACT_LAST_FUSED 3     // the last activation that the products' epilogues take
+#define VLRF_ACT_SILU 4           // x * sigmoid(x): vlrf_gate_mul only
+#define VLRF_ACT_SIGMOID 5        // vlrf_gate_mul only
 
 #define VLRF_DEVERR_TOKEN_RANGE 1
 #define VLRF_DEVERR_POSITION_RANGE 2
@@ -163,6 +167,66 @@ int vlrf_attn_decode_noalloc(const void* qkv, int dtype, int ld, int q_off, cons
                              const int* block_table, int max_blocks, const int* tok_slot, const int* tok_pos, void* out,
                              int ld_out, int rows, int H, int Hkv, int dh, int BT, float scale, int window, int n_split,
                              int* dev_err, cudaStream_t stream);
+
+// ---- RMS norm in groups and row-wise helpers (norm_rms.cu) ----------------------------------------------------------
+// out[r] (+)= y[rows ? rows[r] : r] / sqrt(mean over the column's group of y² + eps) · w: a row's d columns are cut
+// into `groups` equal consecutive parts with a root mean square each (groups = 1: the plain RMS norm).  y float32 of
+// row stride ld_y; out of out_dtype and row stride ld_out; accumulate (float32 out only) adds to the row instead of
+// replacing it.  out may be y.
+int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w, void* out, int out_dtype, int ld_out,
+                       int n_rows, int d, int groups, float eps, int accumulate, cudaStream_t stream);
+// n float32 numbers to out_dtype.
+int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
+// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU or VLRF_ACT_SIGMOID, all three of `dtype` with row strides of
+// their own (out may be a or b).
+int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int dtype, int rows, int cols, int act,
+                  cudaStream_t stream);
+
+// ---- products per head and per group (gemm_heads.cu) ------------------------------------------------------------------
+// Y[m][h·y_hs …] = X[m][h·x_hs …] · W[h]ᵀ for every head h < H; W [H][N][K].
+int vlrf_gemm_heads(const void* X, int ldx, int x_hs, const void* W, void* Y, int ldy, int y_hs, int M, int N, int K, int H,
+                    int in_dtype, int out_dtype, cudaStream_t stream);
+// Rows offsets[g] … offsets[g+1]−1 of X [P][K] times W[g]ᵀ ([G][N][K]) into the same rows of Y [P][N]; offsets
+// (G + 1 entries, ascending, offsets[G] ≤ P) on the device.
+int vlrf_gemm_grouped(const void* X, const void* W, void* Y, const int* offsets, int G, int P, int N, int K, int in_dtype,
+                      int out_dtype, cudaStream_t stream);
+
+// ---- attention over a cache of latents (attention_latent.cu) -----------------------------------------------------------
+// The cache of one layer is [n_blocks][BT][row_w] of `dtype`: per token a row [c | r], the normed latent (C numbers)
+// and a rotated key part shared by all heads (R numbers, R may be 0).  Rotation: of the first rot_dims entries, entry
+// i pairs with entry i + rot_dims/2; angle = position · inv_freq[i] (float32 table of rot_dims/2 entries).
+// proj: float32 [T][ld], columns 0…C−1 the latent before its RMS norm (weight norm_w, eps), C…C+R−1 the key part
+// before its rotation; the token's row is written at (tok_slot, tok_pos).
+int vlrf_latent_append(const float* proj, int ld, int C, int R, const float* norm_w, float eps, const float* inv_freq,
+                       int rot_dims, void* cache, int dtype, int row_w, const int* block_table, int max_blocks,
+                       const int* tok_slot, const int* tok_pos, int T, int BT, int* dev_err, cudaStream_t stream);
+// q: float32 [T][ld_q], per head [dim | R].  qn [T][ld_qn]: the heads' first dim columns, compact; qp [T][ld_qp]:
+// per head a row of C + R columns whose last R receive the rotated part (the first C are left for vlrf_gemm_heads).
+int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims, const int* tok_pos,
+                       void* qn, int ld_qn, void* qp, int ld_qp, int C, int dtype, int T, cudaStream_t stream);
+// qp [T][ld_q]: per head C + R numbers (the query in latent space, then its rotated part).  out [T][ld_out]: per head
+// the C numbers Σ_j p_j c_j with p = softmax_j((qp_h · row_j) · scale) over the visible rows j ≤ position (and, with
+// window > 0, position − j < window).  Any mix of tokens; rows with slot −1 get zeros.  C ≤ 1024.
+int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void* cache, int row_w, int C, int R, const int* block_table,
+                     int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int BT,
+                     float scale, int window, int* dev_err, cudaStream_t stream);
+
+// ---- routed experts (moe.cu) ---------------------------------------------------------------------------------------
+// z: float32 router logits [T][ld_z] (column E: the logit of a shared expert's gate, if shared_gate).  ids, wts, rank
+// [T][top]: the chosen experts (largest logits, ties to the lower index; −1 for padding rows), the softmax over the
+// chosen logits, the pair's rank among its expert's rows; gate [T] = sigmoid(z[t][E]); counts int32 [E], zero before.
+int vlrf_moe_route(const float* z, int ld_z, int E, int top, int shared_gate, const int* tok_slot, int* ids, float* wts,
+                   int* rank, float* gate, int* counts, int T, cudaStream_t stream);
+// offsets[e] = Σ counts[< e], E + 1 entries; counts are left zero.
+int vlrf_moe_plan(int* counts, int* offsets, int E, cudaStream_t stream);
+// sorted[offsets[ids[p]] + rank[p]] = h[p / top] for every pair p < T·top with an expert; row_of[p] = that row or −1.
+int vlrf_moe_gather(const void* h, int dtype, int width, const int* ids, const int* rank, const int* offsets, void* sorted,
+                    int* row_of, int T, int top, cudaStream_t stream);
+// y[t] = Σ_j wts[t][j] · expert_out[row_of[t][j]] (+ (gate ? gate[t] : 1) · shared_out[t] if shared_out) (+ residual[t]
+// if residual, which may be y), float32.
+int vlrf_moe_combine(const float* expert_out, int width, const int* row_of, const float* wts, int top,
+                     const float* shared_out, const float* gate, const float* residual, float* y, int T,
+                     cudaStream_t stream);
 
 // ---- sampling (sampling.cu) ----------------------------------------------------------------------------------------
 // One token per row of float32 logits [n_rows][ld] over V entries, in the order of the reference (include/model/

@@ -1,2 +1,3 @@
 """Architectures.  Importing this package registers them."""
 from . import gpt2  # noqa: F401
+from . import kuvusun  # noqa: F401

@@ -50,3 +50,37 @@ class PreNormBlock:
             self.feed_forward.forward(self.norm2(x, h), x, ctx)
         if not getattr(self.feed_forward, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
+
+
+@register_part("block", "sublayer_norm")
+class SublayerNormBlock:
+    """x += norm1(mixer(x)); x += norm2(ffn(x)): the norm acts on each sublayer's output, and the sublayers read the
+    residual stream itself (rounded to the activation dtype where that is not float32).  The stream and the norm are
+    float32; the sublayer writes its float32 output into scratch (`accumulate=False`), and the norm adds to x.
+    Either sublayer may be absent (None)."""
+
+    leaves_row_stats = False
+
+    def __init__(self, norm1, mixer, norm2, feed_forward):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+
+    def cache_need(self):
+        return self.mixer.cache_need() if self.mixer is not None else None
+
+    def _input(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if ctx.act_dtype == torch.float32:
+            return x
+        from ..csrc import ops
+        h = ctx.ws.get("block_input", ctx.n_tokens, x.shape[1], ctx.act_dtype)
+        ops.cast_rows(x, h, ctx.n_tokens)
+        return h
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+        ctx.ws.row_stats.forget()
+        y = ctx.ws.get("block_sublayer_out", ctx.n_tokens, x.shape[1], torch.float32)
+        if self.mixer is not None:
+            self.mixer.forward(self._input(x, ctx), y, ctx, view, writes_cache, accumulate=False)
+            self.norm1(y, x, accumulate=True)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(self._input(x, ctx), y, ctx, accumulate=False)
+            self.norm2(y, x, accumulate=True)

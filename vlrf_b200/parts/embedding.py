@@ -11,8 +11,10 @@ class TokenEmbedding:
     """x[t] = weight[token[t]], fused with a position encoding that acts at the embedding
     (reference: include/model/ops.hpp:615-626, include/model/transformer.hpp:340)."""
 
-    def __init__(self, weight: torch.Tensor, position=None):
+    def __init__(self, weight: torch.Tensor, position=None, norm=None):
+        """norm: a norm part applied to the embedded rows in place (float32), or None."""
         self.weight = weight
+        self.norm = norm
         self.vocab_size, self.width = weight.shape
         if position is not None and getattr(position, "where", None) == "embedding":
             if position.table.shape[1] != self.width or position.table.dtype != weight.dtype:
@@ -21,16 +23,25 @@ class TokenEmbedding:
         else:
             self.position = None
 
-    #: the rows are written by a kernel that is handed the step's row statistics (see parts/block.py)
-    leaves_row_stats = True
+    @property
+    def leaves_row_stats(self) -> bool:
+        """The rows are written by a kernel that is handed the step's row statistics (see parts/block.py); a norm
+        behind it rewrites them."""
+        return self.norm is None
 
     def emit_decode(self, program, x: torch.Tensor) -> None:
+        if self.norm is not None:
+            from .program import NotFusable
+            raise NotFusable("an embedding with a norm behind it is not an operation of the decode program")
         program.embed(self.weight, self.position.table if self.position is not None else None, x)
 
     def __call__(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         table = self.position.table if self.position is not None else None
         ops.embed(self.weight, table, ctx.tokens, ctx.tok_pos if table is not None else None, x, ctx.dev_err,
                   stats=ctx.ws.row_stats)
+        if self.norm is not None:
+            ctx.ws.row_stats.forget()
+            self.norm(x, x)
         return x
 
 

@@ -12,13 +12,14 @@ from ..csrc import ops
 from .context import StepContext
 from .registry import register_part
 
-ACTIVATIONS = ("gelu_tanh", "gelu_erf")
+ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu2")
 
 
 @register_part("feed_forward", "dense_mlp")
 class DenseMLP:
-    """x += act(h·W_inᵀ + b_in)·W_outᵀ + b_out; the activation runs in the first product's epilogue and
-    the residual sum in the second's (reference: include/model/feedforward.hpp:50-77,
+    """x += act(h·W_inᵀ + b_in)·W_outᵀ + b_out (the biases may be None; act: the two GELUs, or "relu2", the square
+    of relu); with `accumulate=False` the result replaces x instead (blocks that norm it before the sum).  The
+    activation runs in the first product's epilogue and the residual sum in the second's (reference: include/model/feedforward.hpp:50-77,
     include/model/transformer_block.hpp:158; tanh GELU include/model/ops.hpp:390-403)."""
 
     def __init__(self, w_in, b_in, w_out, b_out, *, activation: str):
@@ -42,7 +43,7 @@ class DenseMLP:
         program.product(x, self.w_in, self.b_in, u, norm=norm_terms(norm), act=self.activation)
         program.product(u, self.w_out, self.b_out, x, residual=x)
 
-    def forward(self, h, x: torch.Tensor, ctx: StepContext, norm=None) -> None:
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, norm=None, accumulate: bool = True) -> None:
         T = ctx.n_tokens
         u = ctx.ws.get("ffn_inner", T, self.inner, ctx.act_dtype)
         if h is None and getattr(norm, "fusable_as", None) == "layernorm" and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype):
@@ -52,4 +53,4 @@ class DenseMLP:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
             ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
-        ops.linear(u, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)
+        ops.linear(u, self.w_out, self.b_out, x, residual=x if accumulate else None, stats=ctx.ws.row_stats)

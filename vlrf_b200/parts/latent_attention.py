@@ -1,0 +1,119 @@
+"""Attention whose cache holds one latent per token instead of keys and values.
+
+A token's cache row is [c | r]: the normed latent c (`kv_rank` numbers), from which every head's unrotated key and
+its value are linear maps (k_h = Uk_h c, v_h = Uv_h c), and optionally a rotated key part r (`rot_dim` numbers) that
+all heads share.  Per head
+
+    score(p, j) = (q_h(p) · Uk_h c_j + qr_h(p) · r_j) · scale,     out_h(p) = Uv_h Σ_j softmax_j(score) c_j.
+
+The kernels never form keys or values: the query is carried into the latent space (q'_h = Uk_hᵀ q_h, a product per
+head), every head attends the rows themselves, and the head's result is carried back by Uv_h (another product per
+head).  That is the same arithmetic with the sums taken in another order.
+
+What is a parameter: how queries are made (directly, h·W_qᵀ, or through a latent of their own, RMSnorm(h·W_dqᵀ)·W_uqᵀ);
+the rotated part and its rotation (a position part that acts on q/k, or none); a sigmoid gate on the merged heads
+(W_g, from the same input); whether the layer owns a cache row (W_dkv and its norm) or reads another layer's, as the
+model's schedule says (`writes_cache=False`: it then has no W_dkv and uses the rows as they lie in the cache).
+Norms, rotation angles, scores and softmax are float32; products take operands in the activation dtype.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import LatentNeed
+from ..csrc import ops
+from .context import StepContext
+from .registry import register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention:
+    def __init__(self, *, n_heads: int, dim: int, vdim: int, kv_rank: int, rot_dim: int = 0, scale: float,
+                 w_uk, w_uv, w_out, w_q=None, w_dq=None, dq_norm=None, w_uq=None, w_dkv=None, dkv_norm=None,
+                 w_gate=None, rotary=None, eps: float = 1e-5, window: int = 0):
+        H, C, R = int(n_heads), int(kv_rank), int(rot_dim)
+        per_q = dim + R
+        if (w_q is None) == (w_dq is None):
+            raise ValueError("latent attention: queries come from W_q or from W_dq, its norm and W_uq, not both or neither")
+        if w_q is not None and tuple(w_q.shape)[0] != H * per_q:
+            raise ValueError(f"latent attention: W_q has {w_q.shape[0]} rows, {H * per_q} expected")
+        if w_dq is not None:
+            if dq_norm is None or w_uq is None or w_uq.shape[1] != w_dq.shape[0] or dq_norm.shape[0] != w_dq.shape[0]:
+                raise ValueError("latent attention: the query latent, its norm and W_uq do not chain")
+            if w_uq.shape[0] != H * per_q:
+                raise ValueError(f"latent attention: W_uq has {w_uq.shape[0]} rows, {H * per_q} expected")
+        if tuple(w_uk.shape) != (H * dim, C) or tuple(w_uv.shape) != (H * vdim, C):
+            raise ValueError("latent attention: W_uk is [heads·dim, kv_rank] and W_uv [heads·vdim, kv_rank]")
+        if w_out.shape[1] != H * vdim:
+            raise ValueError("latent attention: the output projection does not take the merged heads")
+        if w_dkv is not None and (w_dkv.shape[0] != C + R or dkv_norm is None or dkv_norm.shape[0] != C):
+            raise ValueError(f"latent attention: W_dkv has kv_rank + rot_dim = {C + R} rows and a norm weight of {C}")
+        if w_gate is not None and w_gate.shape[0] != H * vdim:
+            raise ValueError("latent attention: the gate has one row per merged column")
+        if R > 0:
+            if rotary is None or getattr(rotary, "where", None) != "qk" or rotary.dims > R:
+                raise ValueError("latent attention: a rotated part needs a rotation of at most its own size")
+        if C > ops.LATENT_MAX_RANK:
+            raise ValueError(f"latent attention: a latent of {C} numbers is wider than the {ops.LATENT_MAX_RANK} the kernels hold")
+        self.n_heads, self.dim, self.vdim, self.kv_rank, self.rot_dim = H, int(dim), int(vdim), C, R
+        self.scale, self.eps, self.window = float(scale), float(eps), int(window)
+        self.w_q, self.w_dq, self.dq_norm, self.w_uq = w_q, w_dq, dq_norm, w_uq
+        self.w_dkv, self.dkv_norm, self.w_gate, self.w_out = w_dkv, dkv_norm, w_gate, w_out
+        self.rotary = rotary if R > 0 else None
+        # Uk per head, transposed once: [H, kv_rank, dim], the operand that carries a head's query into latent space;
+        # Uv per head as it is stored: [H, vdim, kv_rank]
+        self.w_uk_t = w_uk.view(H, dim, C).transpose(1, 2).contiguous()
+        self.w_uv = w_uv.view(H, vdim, C)
+
+    def cache_need(self):
+        if self.window > 0:
+            return LatentNeed(self.kv_rank + self.rot_dim, "window", self.window)
+        return LatentNeed(self.kv_rank + self.rot_dim)
+
+    fuses_norm = False
+    leaves_row_stats = False
+
+    def kernels(self, act_dtype: torch.dtype, block_tokens: int) -> dict:
+        kind = ops.attention_latent_kind(act_dtype, self.kv_rank, self.rot_dim)
+        return {"prompt": kind["prompt"], "decode": kind["decode"]}
+
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, accumulate: bool = True) -> None:
+        T, ws, act = ctx.n_tokens, ctx.ws, ctx.act_dtype
+        H, dim, vdim, C, R = self.n_heads, self.dim, self.vdim, self.kv_rank, self.rot_dim
+        D = C + R
+        inv_freq = self.rotary.inv_freq if self.rotary is not None else None
+        rot_dims = self.rotary.dims if self.rotary is not None else 0
+        if writes_cache:
+            if self.w_dkv is None:
+                raise ValueError("latent attention: a layer without W_dkv reads another layer's cache and cannot write one")
+            proj = ws.get("latent_kv_proj", T, D, torch.float32)
+            ops.linear(h, self.w_dkv, None, proj)
+            ops.latent_append(proj, C, R, self.dkv_norm, self.eps, inv_freq, rot_dims, view.rows, view.block_table,
+                              ctx.tok_slot, ctx.tok_pos, T, ctx.dev_err)
+        # queries: per head [dim | R]
+        q_in, w_qproj = h, self.w_q
+        if self.w_dq is not None:
+            cq32 = ws.get("latent_cq32", T, self.w_dq.shape[0], torch.float32)
+            ops.linear(h, self.w_dq, None, cq32)
+            q_in = ws.get("latent_cq", T, self.w_dq.shape[0], act)
+            ops.group_rmsnorm(cq32, self.dq_norm, self.eps, 1, q_in)
+            w_qproj = self.w_uq
+        qp = ws.get("latent_qp", T, H * D, act)
+        qn = ws.get("latent_qn", T, H * dim, act)
+        if R == 0:
+            ops.linear(q_in, w_qproj, None, qn)
+        else:
+            q32 = ws.get("latent_q32", T, H * (dim + R), torch.float32)
+            ops.linear(q_in, w_qproj, None, q32)
+            ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
+        ops.linear_heads(qn.view(T, H, dim), self.w_uk_t, qp.view(T, H, D)[:, :, :C], T)
+        o = ws.get("latent_o", T, H * C, act)
+        ops.attention_latent(qp, view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, o, T, H, self.scale,
+                             self.window, ctx.dev_err, ctx=ctx)
+        merged = ws.get("attn_out", T, H * vdim, act)
+        ops.linear_heads(o.view(T, H, C), self.w_uv, merged.view(T, H, vdim), T)
+        if self.w_gate is not None:
+            g = ws.get("latent_gate", T, H * vdim, act)
+            ops.linear(h, self.w_gate, None, g)
+            ops.gate_mul(g, merged, merged, "sigmoid", T, H * vdim)
+        ops.linear(merged, self.w_out, None, x, residual=x if accumulate else None)

@@ -11,6 +11,7 @@ Interface of a mixer (what `Block` and the step rely on):
         ctx   StepContext        tokens' slots and positions, scratch, error word
         view  CacheView | None   this layer's storage (another layer's when the layer list says so;
                                  then writes_cache is False and the mixer only reads it)
+        (accumulate=False: x receives mix(h) instead of growing by it, for blocks that norm a sublayer's output)
 """
 from __future__ import annotations
 
@@ -68,7 +69,8 @@ class CausalSelfAttention:
     #: what those say afterwards is true (the block forgets them after parts that do not declare this)
     leaves_row_stats = True
 
-    def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, norm=None) -> None:
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, norm=None,
+                accumulate: bool = True) -> None:
         T = ctx.n_tokens
         qkv = ctx.ws.get("attn_qkv", T, self.qkv_width, ctx.act_dtype)
         appended = False
@@ -94,7 +96,7 @@ class CausalSelfAttention:
                           ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
         merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
         self._attend(qkv, view, merged, ctx)
-        ops.linear(merged, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)
+        ops.linear(merged, self.w_out, self.b_out, x, residual=x if accumulate else None, stats=ctx.ws.row_stats)
 
     def emit_decode(self, program, x: torch.Tensor, norm, view, writes_cache: bool = True) -> None:
         """The decode step of this mixer as operations of a decode program: norm + q/k/v projection (+ cache

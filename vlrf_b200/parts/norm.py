@@ -26,3 +26,21 @@ class LayerNorm:
         """out[r] = LN(x[rows[r]]) when `rows` is given, else row by row."""
         ops.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out
+
+
+@register_part("norm", "group_rmsnorm")
+class GroupRMSNorm:
+    """The row is cut into `groups` equal consecutive parts; each part is divided by sqrt(mean(part²) + eps) of its
+    own, and the whole row is multiplied by weight.  One group is the plain RMS norm.  Sums and the division are
+    float32.  `accumulate=True` adds the result to the (float32) output rows instead of replacing them, which is
+    what a block needs that norms a sublayer's output before the residual sum."""
+
+    def __init__(self, weight: torch.Tensor, eps: float, groups: int = 1):
+        if weight.dim() != 1 or groups < 1 or weight.shape[0] % groups != 0:
+            raise ValueError(f"GroupRMSNorm: {tuple(weight.shape)} weights cannot be cut into {groups} equal parts")
+        self.weight, self.eps, self.groups = weight, float(eps), int(groups)
+        self.width = weight.shape[0]
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows, accumulate)
+        return out

@@ -24,3 +24,21 @@ class LearnedAbsolutePositions:
             raise ValueError("LearnedAbsolutePositions: the table is [positions, width]")
         self.table = table
         self.max_positions = table.shape[0]
+
+
+@register_part("position", "rotary")
+class RotaryPositions:
+    """Rotation of queries and keys by position.  Of a vector's first `dims` entries, entry i is paired with entry
+    i + dims/2; at position p the pair (u, v) becomes (u cos a − v sin a, v cos a + u sin a) with a = p · f_i and
+    f_i = base^(−2i/dims); entries beyond `dims` pass unchanged.  The part holds the table f (float32, made in 64-bit);
+    the mixer that is given the part applies it inside its own kernels, with angles in float32."""
+
+    where = "qk"
+
+    def __init__(self, base: float, dims: int, device):
+        if dims <= 0 or dims % 2 != 0 or not base > 0.0:
+            raise ValueError(f"RotaryPositions: {dims} dimensions cannot be rotated in pairs, or base {base} is not positive")
+        self.base, self.dims = float(base), int(dims)
+        half = dims // 2
+        f = torch.tensor([self.base ** (-2.0 * i / dims) for i in range(half)], dtype=torch.float64)
+        self.inv_freq = f.to(torch.float32).to(device).contiguous()

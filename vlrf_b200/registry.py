@@ -3,7 +3,7 @@
 An entry holds the configuration class that reads the architecture's
 config.json, the function that lists the tensors a checkpoint must hold, the
 function that draws random weights, and the function that assembles the model
-from parts.  `model_type` in config.json selects the entry everywhere in the
+from parts.  `model_type` (or `architecture`) in config.json selects the entry everywhere in the
 framework: loading, random-weights mode, trace replay, the command line.
 
 The reference has no such table: it guesses the architecture from names in its
@@ -72,10 +72,10 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_of(config_dict: dict) -> Architecture:
-    """The entry that a config.json's `model_type` names."""
-    mt = config_dict.get("model_type")
+    """The entry that a config.json's `model_type` (or, in configurations that spell it so, `architecture`) names."""
+    mt = config_dict.get("model_type", config_dict.get("architecture"))
     if not isinstance(mt, str) or not mt:
-        raise ConfigError("config.json has no 'model_type'; registered: " + ", ".join(architecture_names()))
+        raise ConfigError("config.json has neither 'model_type' nor 'architecture'; registered: " + ", ".join(architecture_names()))
     return get_architecture(mt)
 
 
