@@ -10,7 +10,9 @@ from vlrf_b200.engine.step import StepEntry
 def poison(engine):
     """Fill every key/value pool with NaN: whatever a kernel reads without having written it shows."""
     for g in engine.cache._groups:
-        if hasattr(g, "k"):
+        if getattr(g, "rows", None) is not None:
+            g.rows.fill_(float("nan"))
+        elif hasattr(g, "k"):
             g.k.fill_(float("nan"))
             g.v.fill_(float("nan"))
 
@@ -71,4 +73,19 @@ def drive_batches(engine, requests, batch_size, prompt_lens):
             out[i] = torch.cat(got[i])
     engine.check_device_errors()
     engine.cache.check()
+    return out
+
+
+def drive_portions(engine, requests, portion):
+    """Each request alone, its tokens in portions of `portion` tokens (the last one shorter)."""
+    out = []
+    for ids in requests:
+        slot = engine.start_sequence()
+        rows = []
+        for at in range(0, len(ids), portion):
+            part = ids[at:at + portion]
+            rows.append(engine.step([StepEntry(slot, part, list(range(len(part))))]).float().cpu().clone())
+        out.append(torch.cat(rows))
+        engine.end_sequence(slot)
+    engine.check_device_errors()
     return out

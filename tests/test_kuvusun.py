@@ -1,0 +1,176 @@
+"""Kuvusun through the engine against the plain implementation: whole requests, the last tokens one by one, prompts in
+portions, unequal batches with reused slots and blocks, the first tokens, long decoding, and greedy generation through
+the package's entry point — in 32-bit and in bfloat16, on four small models whose sizes all differ."""
+import pytest
+import torch
+
+import plain_kuvusun as plain
+from conftest import random_ids, record_error
+from engine_drives import drive_batches, drive_portions, drive_tail_one_by_one, drive_whole, poison
+from kuvusun_models import MODELS, SHARP_FACTOR, write_model
+
+pytestmark = pytest.mark.gpu
+
+#: largest absolute logit error over the largest absolute logit of the plain implementation
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"kuv_a": [1 + 12, 17 + 12, 64 + 12, 65 + 12, 150], "kuv_b": [3 + 10, 63 + 10, 129 + 10, 200],
+           "kuv_odd": [2 + 8, 40 + 8, 100 + 8, 130], "kuv_sharp": [5 + 16, 64 + 16, 127 + 16, 260]}
+DECODE = {"kuv_a": 12, "kuv_b": 10, "kuv_odd": 8, "kuv_sharp": 16}
+NAMES = list(MODELS)
+#: per model and request: the leading positions without a close call of a router (plain.decided_prefix)
+DECIDED: dict = {}
+
+
+@pytest.fixture(scope="module")
+def kuv_dirs(tmp_path_factory):
+    out = {}
+    for i, (name, cfg) in enumerate(MODELS.items()):
+        d = tmp_path_factory.mktemp(name)
+        write_model(cfg, 40 + i, d, sharp=SHARP_FACTOR if name == "kuv_sharp" else 1.0)
+        out[name] = d
+    return out
+
+
+@pytest.fixture(scope="module")
+def truth(kuv_dirs):
+    out = {}
+    for name, d in kuv_dirs.items():
+        cfg, w = plain.read_model_dir(d)
+        reqs = [random_ids(cfg["vocab"], n, 11 + i) for i, n in enumerate(LENGTHS[name])]
+        out[name] = (cfg, w, reqs, [plain.logits_all_positions(cfg, w, ids) for ids in reqs])
+        DECIDED[name] = [plain.decided_prefix(cfg, w, ids) for ids in reqs]
+    return out
+
+
+def make_engine(kuv_dirs, name, dtype, max_tokens):
+    from vlrf_b200.engine import Engine, load_model
+    eng = Engine(load_model(kuv_dirs[name], dtype), max_tokens=max_tokens)
+    poison(eng)
+    return eng
+
+
+def compare(got, want, dtype, what, model, decided=None):
+    """32-bit: every position.  bfloat16: the positions before a router's first close call (`decided`, per request;
+    None: all), since rounding may choose another expert there and later positions may attend that token."""
+    worst = 0.0
+    for i, (g, t) in enumerate(zip(got, want)):
+        assert g.shape == t.shape, f"{what}: request {i} has shape {tuple(g.shape)}, expected {tuple(t.shape)}"
+        assert torch.isfinite(g).all(), f"{what}: request {i} has non-finite logits (something unwritten was read)"
+        err = (g.double() - t).abs().max(dim=1).values / float(t.abs().max())
+        if dtype != "float32" and decided is not None:
+            err = err[:decided[i]]
+            if err.numel() == 0:
+                continue
+        bad = (err > TOL[dtype]).nonzero()
+        assert bad.numel() == 0, (f"{what} ({model}, {dtype}): request {i} (length {len(t)}) first differs at position "
+                                  f"{int(bad[0])} with error {float(err[bad[0]]):.3e} of the logit scale")
+        worst = max(worst, float(err.max()))
+    record_error("kuvusun " + what, model, dtype, worst)
+
+
+def test_the_sharp_model_is_sharp(truth):
+    """Its attention must depend on which keys are seen: hiding the first key moves the logits far beyond rounding."""
+    cfg, w, reqs, want = truth["kuv_sharp"]
+    ids = reqs[1]
+    moved = plain.logits_all_positions(cfg, w, ids[1:])[-1]
+    assert float((moved - want[1][-1]).abs().max() / want[1].abs().max()) > 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(kuv_dirs, truth, name, dtype):
+    _, _, reqs, want = truth[name]
+    eng = make_engine(kuv_dirs, name, dtype, 320)
+    compare(drive_whole(eng, reqs), want, dtype, "whole", name, DECIDED[name])
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_tokens_one_by_one(kuv_dirs, truth, name, dtype):
+    _, _, reqs, want = truth[name]
+    eng = make_engine(kuv_dirs, name, dtype, 320)
+    compare(drive_tail_one_by_one(eng, reqs, 32), want, dtype, "prefix + 32 single tokens", name, DECIDED[name])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("portion", [2, 7, 64, 65])
+def test_prompts_in_portions(kuv_dirs, truth, portion, dtype):
+    for name in ("kuv_a", "kuv_sharp"):
+        _, _, reqs, want = truth[name]
+        eng = make_engine(kuv_dirs, name, dtype, 320)
+        compare(drive_portions(eng, reqs[1:], portion), want[1:], dtype, f"portions of {portion}", name, DECIDED[name][1:])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_with_reused_slots_and_blocks(kuv_dirs, truth, name, dtype):
+    _, _, reqs, want = truth[name]
+    prompt_lens = [max(1, len(r) - DECODE[name]) for r in reqs]
+    batch = 3
+    order = list(reversed(range(len(reqs))))
+
+    def need_of(rs):
+        return max(sum((len(r) + 63) // 64 * 64 for r in rs[b:b + batch]) for b in range(0, len(rs), batch))
+
+    eng = make_engine(kuv_dirs, name, dtype, max(need_of(reqs), need_of([reqs[i] for i in order])))
+    compare(drive_batches(eng, reqs, batch, prompt_lens), want, dtype, "unequal batches", name, DECIDED[name])
+    assert eng.cache.slots.n_held == 0
+    poison(eng)           # what the second round reads it must have written itself
+    got = drive_batches(eng, [reqs[i] for i in order], batch, [prompt_lens[i] for i in order])
+    compare(got, [want[i] for i in order], dtype, "unequal batches, reused cache", name, [DECIDED[name][i] for i in order])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens(kuv_dirs, truth, name, dtype):
+    cfg, w, _, _ = truth[name]
+    reqs = [random_ids(cfg["vocab"], n, 70 + n) for n in (1, 2, 3, 1)]
+    want = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    decided = [plain.decided_prefix(cfg, w, ids) for ids in reqs]
+    eng = make_engine(kuv_dirs, name, dtype, 256)
+    compare(drive_whole(eng, reqs), want, dtype, "first tokens, whole", name, decided)
+    compare(drive_batches(eng, reqs, 4, [1, 1, 1, 1]), want, dtype, "first tokens, batch", name, decided)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_from_one_token(kuv_dirs, truth, dtype):
+    for name in ("kuv_a", "kuv_sharp"):
+        cfg, w, _, _ = truth[name]
+        ids = random_ids(cfg["vocab"], 200, 5)
+        want = plain.logits_all_positions(cfg, w, ids)
+        eng = make_engine(kuv_dirs, name, dtype, 256)
+        compare(drive_tail_one_by_one(eng, [ids], tail=len(ids) - 1), [want], dtype, "decoding 200 positions", name,
+                [plain.decided_prefix(cfg, w, ids)])
+
+
+def test_a_batch_of_seventy_sequences(kuv_dirs, truth):
+    """More rows in a decode step than the few-row products take."""
+    cfg, w, _, _ = truth["kuv_odd"]
+    reqs = [random_ids(cfg["vocab"], 4 + (i * 7) % 30, 300 + i) for i in range(70)]
+    want = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    decided = [plain.decided_prefix(cfg, w, ids) for ids in reqs]
+    for dtype in DTYPES:
+        eng = make_engine(kuv_dirs, "kuv_odd", dtype, 70 * 64)
+        compare(drive_batches(eng, reqs, 70, [max(1, len(r) - 3) for r in reqs]), want, dtype, "seventy sequences", "kuv_odd", decided)
+
+
+@pytest.mark.parametrize("name", ["kuv_a", "kuv_b"])
+def test_greedy_generation_through_the_entry_point(kuv_dirs, truth, name):
+    """Seven requests over three rows: requests wait, take over rows of those that ended, and decode in the replayed
+    session beside padding rows; every request gets what it gets alone from the plain implementation (32-bit, so that
+    no argmax rests on rounding)."""
+    from vlrf_b200.api import Model
+    from vlrf_b200.sampling.params import SamplingParams
+    cfg, w, _, _ = truth[name]
+    prompts = [random_ids(cfg["vocab"], n, 900 + n) for n in (3, 20, 1, 66, 9, 33, 5)]
+    new = [6, 3, 9, 4, 7, 2, 8]
+    model = Model.load(kuv_dirs[name], "float32", max_tokens=3 * 128, n_slots=3)
+    params = [SamplingParams(max_new_tokens=n, do_sample=False) for n in new]
+    results = model.generate_ids(prompts, params)
+    for p, n, r in zip(prompts, new, results):
+        assert r.new_tokens == plain.greedy_generate(cfg, w, p, n)
+    assert model.engine.cache.slots.n_held == 0
+    model.engine.cache.check()
