@@ -296,6 +296,139 @@ def prefill_device(model_dir, dtype="bfloat16", reps=5, replay=True):
     return dict(tokens=n_seq * length, ms=ms, flops=prefill_flops(cfg, [length] * n_seq, n_seq))
 
 
+# ---- a second design beside its closest existing model (--design) ---------------------------------------------------------
+
+#: Kuvusun at two sizes that resemble a real model's layers, each beside a GPT-2 of the same width, depth, heads and
+#: dense inner size.  Layers: queries through a latent + dense feed-forward; rotated part + routed experts; the same
+#: reading the cache of the layer before; queries through a latent + routed experts.
+DESIGN_SIZES = {
+    "s": dict(width=1024, heads=16, dim=64, rot=32, vdim=64, kv_rank=256, q_rank=384, ff=4096, experts=16, top=2,
+              expert_ff=1024, shared_ff=1024, vocab=32000),
+    "m": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=768, ff=8192, experts=32, top=4,
+              expert_ff=1408, shared_ff=2816, vocab=32000),
+}
+
+
+def kuvusun_config(z: dict) -> dict:
+    att1 = {"type": "latent_attention", "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+                                                  "q_rank": z["q_rank"], "scale": z["dim"] ** -0.5}}
+
+    def att2(kv_from=None):
+        m = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "rot_dim": z["rot"],
+             "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention_2", "mixer": m}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    layers = [dict(att1, mlp={"kind": "dense", "ff": z["ff"]}), dict(att2(), mlp=moe), dict(att2(1), mlp=moe), dict(att1, mlp=moe)]
+    return {"architecture": "Kuvusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4}, "layers": layers}
+
+
+def gpt2_config_like(z: dict) -> dict:
+    return dict(model_type="gpt2", n_layer=4, n_embd=z["width"], n_head=z["heads"], n_inner=z["ff"], vocab_size=z["vocab"],
+                n_positions=2048, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+                bos_token_id=0, eos_token_id=0)
+
+
+def design_point(model_dir: str, prompt_len: int, batches, steps: int, warmup: int) -> dict:
+    """Prefill (2 sequences of prompt_len tokens, replayed graph, median of 5) and decode (per batch size: `steps`
+    replayed steps from contexts of prompt_len) of one model, and the device time of every kernel entry point in one
+    prompt step and one decode step launched kernel by kernel."""
+    import numpy as np
+    import torch
+    from vlrf_b200 import log
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.engine import Engine, StepEntry, load_model
+    from vlrf_b200.engine.decode import DecodeSession
+    model = load_model(model_dir, "bfloat16")
+    vocab = model.vocab_size
+    out = {"weights_mib": round(model.weight_bytes() / 2**20, 1)}
+    # prefill
+    engine = Engine(model, max_tokens=2 * prompt_len, n_slots=2)
+    prompts = [np.asarray(p, dtype=np.int32) for p in random_prompts(vocab, 2, prompt_len, 2)]
+    times = []
+    for r in range(8):
+        if r == 7:                      # the last repetition: kernel by kernel, each timed
+            engine.capture_repeated_steps = False
+            log.timers.reset(); log.timers.enable(True)
+        slots = [engine.start_sequence() for _ in range(2)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step([StepEntry(s, p, [prompt_len - 1]) for s, p in zip(slots, prompts)])
+        e1.record()
+        torch.cuda.synchronize()
+        if 2 <= r < 7:
+            times.append(e0.elapsed_time(e1))
+        for s in slots:
+            engine.end_sequence(s)
+    log.timers.enable(False)
+    engine.check_device_errors()
+    out["prefill"] = {"tokens": 2 * prompt_len, "ms": round(statistics.median(times), 4),
+                      "tok_s": round(2 * prompt_len / (statistics.median(times) / 1e3), 1),
+                      "kernels_us": {k: [n, round(1e3 * ms, 1)] for k, n, ms, _ in log.timers.report()}}
+    del engine
+    # decode
+    out["decode"] = {}
+    for batch in batches:
+        engine = Engine(model, max_tokens=batch * (prompt_len + 64 * (2 + (warmup + steps) // 64)), n_slots=batch)
+        prompts = random_prompts(vocab, batch, prompt_len, 1)
+        slots = [engine.start_sequence() for _ in range(batch)]
+        tok = torch.zeros(batch, dtype=torch.int32, device=model.device)
+        for b0 in range(0, batch, 8):
+            idx = list(range(b0, min(batch, b0 + 8)))
+            logits = engine.step([StepEntry(slots[i], prompts[i], [prompt_len - 1]) for i in idx])
+            ops.sample(logits, len(idx), tok[b0:b0 + len(idx)])
+        sess = DecodeSession(engine, slots, use_graph=True)
+        sess.reserve_ahead(warmup + steps + 2)
+        sess.set_tokens(tok)
+        for _ in range(warmup):
+            sess.step_greedy(tok)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            sess.step_greedy(tok)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        # one more step kernel by kernel, each timed
+        plain = DecodeSession(engine, slots, use_graph=False)
+        plain.set_tokens(tok)
+        plain.step_greedy(tok)
+        log.timers.reset(); log.timers.enable(True)
+        plain.step_greedy(tok)
+        log.timers.enable(False)
+        engine.check_device_errors()
+        out["decode"][f"b{batch}"] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / (ms / 1e3), 1),
+                                      "kernels_per_step": sess.kernels_per_step, "cache_mib": round(engine.cache.live_kv_bytes(slots) / 2**20, 1),
+                                      "kernels_us": {k: [n, round(1e3 * t, 1)] for k, n, t, _ in log.timers.report()}}
+        del sess, plain, engine
+    return out
+
+
+def design_bench(args) -> int:
+    """`--design kuvusun`: the design at sizes like a real model's layers (random weights) beside a GPT-2 of equal
+    size: prefill and decode throughput, and each kernel's time.  One JSON line."""
+    import vlrf_b200.models  # noqa: F401
+    from vlrf_b200.weights import write_random_model
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    line = {"design": args.design, "beside": "gpt2", "dtype": "bf16", "data": "synthetic (seeded random token ids, random weights)",
+            "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": {}}
+    for name in args.design_sizes.split(","):
+        z = DESIGN_SIZES[name]
+        point = {"sizes": z}
+        with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
+            for label, cfg in (("kuvusun", kuvusun_config(z)), ("gpt2", gpt2_config_like(z))):
+                d = str(write_random_model(cfg, 1234, os.path.join(tmp, label)))
+                point[label] = design_point(d, args.design_prompt, [8, 64], max(8, min(args.steps, 64)), max(3, min(args.warmup, 8)))
+        line["sizes"][name] = point
+    print(json.dumps(line))
+    return 0
+
+
+
 def metric_label(preset: str, batch: int, first_context: int, last_context: int) -> str:
     sizes = "GPT-2 small sizes" if preset == "gpt2" else preset
     return f"decode tokens/s ({sizes}, batch {batch}, contexts {first_context} to {last_context})"
@@ -340,10 +473,16 @@ def main() -> int:
                     help="with --only decode or prefill and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
+    ap.add_argument("--design", default=None, choices=["kuvusun"],
+                    help="instead of the default workload: this design at sizes like a real model's layers beside a GPT-2 of equal size")
+    ap.add_argument("--design-sizes", default="s,m", help="with --design: which of the sizes %s" % ",".join(DESIGN_SIZES))
+    ap.add_argument("--design-prompt", type=int, default=1024, help="with --design: tokens of each of the two prompts, and the decode steps' first context")
     args = ap.parse_args()
 
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design is not None:
+        return design_bench(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for --gpus {args.gpus})")
         return 2

@@ -105,10 +105,11 @@ def route(z, top):
 def routed_ff(h, w, prefix, ml, margins=None):
     z = h @ w[prefix + "router"].T + w[prefix + "router.b"]
     idx, wt = route(z, ml["router"]["top"])
-    if margins is not None:          # by how much the last chosen logit beats the first one left out, per token
-        top = ml["router"]["top"]
+    if margins is not None:          # by how much the last chosen logit beats the first one left out, per token,
+        top = ml["router"]["top"]    # over the size of the token's logits (an error of rounding grows with them)
         s = torch.sort(z, dim=-1, descending=True).values
-        margins.append(s[:, top - 1] - s[:, top] if top < z.shape[1] else torch.full((z.shape[0],), float("inf"), dtype=z.dtype))
+        size = z.abs().max(dim=-1).values.clamp_min(1.0)
+        margins.append((s[:, top - 1] - s[:, top]) / size if top < z.shape[1] else torch.full((z.shape[0],), float("inf"), dtype=z.dtype))
     y = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(idx.shape[1]):
@@ -146,7 +147,7 @@ def logits_all_positions(cfg, w, ids):
 
 def decided_prefix(cfg, w, ids, least=0.05):
     """How many leading positions of a request are free of close calls of any router: up to the first token whose
-    last chosen logit beats the first one left out by less than `least`.  An implementation that rounds differently
+    last chosen logit beats the first one left out by less than `least` of the size of its logits.  An implementation that rounds differently
     may choose other experts there, and everything after may attend that token."""
     margins = []
     hidden_all_positions(cfg, w, ids, margins=margins)

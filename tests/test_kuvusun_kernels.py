@@ -212,6 +212,73 @@ def plain_rows_attention(q, rows, C, scale, pos, window=0):
     return torch.softmax(s, -1) @ rows[first:pos + 1, :C].double()
 
 
+def step_tables(positions, runs, splits=None):
+    """What a step hands to the attention kernels besides each token's slot and position: its sequence tables.
+    `runs`: how many consecutive tokens each sequence of the step brings (all of slot 1)."""
+    import types
+    from vlrf_b200.parts.context import Workspace
+    starts = [0]
+    for n in runs:
+        starts.append(starts[-1] + n)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    return types.SimpleNamespace(max_new=max(runs), n_seqs=len(runs), seq_slot=t([1] * len(runs)), seq_start=t(starts),
+                                 seq_pos0=t([positions[a] for a in starts[:-1]]), max_context=max(positions) + 1,
+                                 ws=Workspace("cuda"))
+
+
+@pytest.mark.parametrize("C,R,H", [(64, 0, 2), (512, 64, 2), (32, 16, 9), (96, 16, 20), (256, 32, 16)])
+@pytest.mark.parametrize("splits", [None, 1, 3, 16])
+def test_tensor_core_attention_over_latent_rows(C, R, H, splits, monkeypatch):
+    """The tensor-core kernel against the plain attention: a prompt's portion (consecutive tokens of one sequence that
+    begin in the middle of a block and cross borders, with more and fewer tokens than a CTA takes), and single tokens
+    whose contexts are cut into parts (more parts than some contexts have tiles).  One key per head stands out."""
+    from vlrf_b200.csrc import ops
+    if splits is not None:
+        monkeypatch.setenv("VLRF_B200_DECODE_SPLITS", str(splits))
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(C + H)
+    n, D, scale = 700, C + R, 0.37
+    rows = torch.randn(n, D, generator=g).to(dt)
+    order = [5, 2, 9, 0, 7, 1, 3, 4, 6, 8, 10]
+    cache, table = paged(12, order, D, dt)
+    for b in range(11):
+        cache[order[b], :min(64, n - 64 * b)] = rows[64 * b:64 * b + 64].cuda()
+    if splits is None:
+        positions, runs = list(range(59, 59 + 75)) + list(range(0, 3)) + [690], [75, 3, 1]       # portions of a prompt
+    else:
+        positions = [699, 0, 31, 32, 63, 64, 65, 300, 1, 127]                                  # single tokens
+        runs = [1] * len(positions)
+    stars = [(7 * i + 3) % (p + 1) if i % 3 else p - min(p, i % 5) for i, p in enumerate(positions)]
+    qp = torch.zeros(len(positions), H * D, dtype=dt)
+    for i, (pos, star) in enumerate(zip(positions, stars)):
+        for h in range(H):
+            k = rows[(star + 11 * h) % (pos + 1)].float()
+            qp[i, h * D:(h + 1) * D] = (k * (30.0 / (scale * float(k @ k)))).to(dt) + (0.05 * torch.randn(D, generator=g)).to(dt)
+    ctx = step_tables(positions, runs)
+    assert ops.attention_latent_kind(dt, C, R)["decode"] == "mma.sync"
+    pos_t = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    slot = torch.ones(len(positions), dtype=torch.int32, device="cuda")
+    out = torch.full((len(positions), H * C), float("nan"), dtype=dt, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.attention_latent(qp.cuda(), cache, C, R, table, slot, pos_t, out, len(positions), H, scale, 0, err, ctx=ctx)
+    assert int(err.item()) == 0
+    general = torch.zeros_like(out)
+    ops.attention_latent(qp.cuda(), cache, C, R, table, slot, pos_t, general, len(positions), H, scale, 0, err)
+    for i, pos in enumerate(positions):
+        want = plain_rows_attention(qp[i].view(H, D), rows, C, scale, pos)
+        close(out[i].view(H, C), want, 1.2e-2, f"token {i} at {pos}")
+        close(out[i].view(H, C), general[i].view(H, C), 1.2e-2, f"token {i} at {pos} against the general kernel")
+    if splits is None:        # a window, whose edge falls inside a tile for some tokens and on its border for others
+        for window in (33, 64):
+            ops.attention_latent(qp.cuda(), cache, C, R, table, slot, pos_t, out, len(positions), H, scale, window, err, ctx=ctx)
+            for i, pos in enumerate(positions):
+                close(out[i].view(H, C), plain_rows_attention(qp[i].view(H, D), rows, C, scale, pos, window), 1.2e-2, f"window {window}, token at {pos}")
+    # padding sequences give zeros
+    ctx.seq_slot[0] = -1
+    ops.attention_latent(qp.cuda(), cache, C, R, table, slot, pos_t, out, len(positions), H, scale, 0, err, ctx=ctx)
+    assert float(out[:runs[0]].float().abs().max()) == 0.0 and int(err.item()) == 0
+
+
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("C,R,H", [(40, 8, 3), (36, 6, 5), (64, 0, 2), (512, 64, 2), (24, 16, 9)])
 def test_attention_over_latent_rows_finds_a_key_that_stands_out(C, R, H, dt):

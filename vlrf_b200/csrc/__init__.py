@@ -99,6 +99,11 @@ _SIGNATURES = {
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "vlrf_attn_latent": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
+    "vlrf_attn_latent_mma_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_attn_latent_mma_group": [_c_int, _c_int],
+    "vlrf_attn_latent_mma": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
+                             _c_void_p, _c_void_p],
     "vlrf_moe_route": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_void_p],
     "vlrf_moe_plan": [_c_void_p, _c_void_p, _c_int, _c_void_p],

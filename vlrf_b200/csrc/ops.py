@@ -640,21 +640,54 @@ def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, to
 LATENT_MAX_RANK = 1024
 
 
+LATENT_ATTENTION_MMA = True          # off: every step takes the general kernel (for measurements and cross-checks)
+
+
+def _latent_mma_takes(dtype: torch.dtype, C: int, R: int, row_w: int, block_tokens: int, ld_q: int) -> bool:
+    if dtype != torch.bfloat16 or not LATENT_ATTENTION_MMA:
+        return False
+    from . import library
+    return bool(library().vlrf_attn_latent_mma_takes(C, R, row_w, block_tokens, ld_q))
+
+
 def attention_latent_kind(dtype: torch.dtype, C: int, R: int) -> dict:
-    """Which kernels attention over a latent cache of these sizes runs on."""
-    return {"prompt": "CUDA cores", "decode": "CUDA cores"}
+    """Which kernels attention over a latent cache of these sizes runs on: "mma.sync" or "CUDA cores"."""
+    kind = "mma.sync" if _latent_mma_takes(dtype, C, R, C + R, 64, 8) else "CUDA cores"
+    return {"prompt": kind, "decode": kind}
+
+
+def latent_decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
+    """Into how many parts a decode step cuts each context over a latent cache: about two CTAs an SM in all, parts of
+    at least 128 rows."""
+    forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
+    if forced:
+        return max(1, min(16, int(forced)))
+    ctas = max(1, n_rows * ((n_heads + 15) // 16))
+    return max(1, min(16, -(-2 * sm_count() // ctas), -(-max_context // 128)))
 
 
 def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, scale: float,
                      window: int, dev_err, ctx=None) -> None:
     """Each token's heads (queries in latent space, [T, H·(C + R)]) attend the rows 0…position of the token's slot in
-    the latent cache [block, BT, row]; out [T, H·C] receives Σ_j p_j c_j per head."""
+    the latent cache [block, BT, row]; out [T, H·C] receives Σ_j p_j c_j per head.  With the step's context (`ctx`:
+    its sequence tables and scratch) bfloat16 steps of sizes that the tensor-core kernel takes run there."""
     _dev(qp, "qp"); _dev(cache, "cache", qp.dtype); _dev(out, "out", qp.dtype)
     _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
     _dev(tok_pos, "tok_pos", torch.int32); _dev(dev_err, "dev_err", torch.int32)
     if qp.shape[1] != n_heads * (C + R) or out.shape[1] != n_heads * C or cache.shape[2] < C + R \
             or min(qp.shape[0], out.shape[0]) < n_tokens:
         raise KernelError("attention_latent: sizes do not match")
+    if ctx is not None and _latent_mma_takes(qp.dtype, C, R, cache.shape[2], cache.shape[1], qp.shape[1]):
+        n_split, partials = 1, None
+        if ctx.max_new == 1:
+            n_split = latent_decode_splits(ctx.n_seqs, n_heads, ctx.max_context)
+            if n_split > 1:
+                partials = ctx.ws.get("latent_attn_partials", ctx.n_seqs * ((n_heads + 15) // 16) * n_split * 16, C + 2, torch.float32)
+        call("vlrf_attn_latent_mma", _ptr(qp), qp.shape[1], _ptr(cache), cache.shape[2], C, R, _ptr(block_table),
+             block_table.shape[1], _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(out), out.shape[1],
+             ctx.n_seqs, ctx.max_new, n_heads, cache.shape[1], float(scale), int(window), n_split, _ptr(partials),
+             _ptr(dev_err), _stream())
+        return
     call("vlrf_attn_latent", _ptr(qp), dtype_code(qp.dtype), qp.shape[1], _ptr(cache), cache.shape[2], C, R, _ptr(block_table),
          block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_tokens, n_heads, cache.shape[1],
          float(scale), int(window), _ptr(dev_err), _stream())

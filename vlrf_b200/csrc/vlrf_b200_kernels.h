@@ -210,6 +210,18 @@ int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const fl
 int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void* cache, int row_w, int C, int R, const int* block_table,
                      int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int BT,
                      float scale, int window, int* dev_err, cudaStream_t stream);
+// The same on the tensor cores (`mma.sync`, bfloat16; attention_latent_mma.cu): a token's heads are the rows of the
+// MMAs, tiles of 32 cache rows lie in shared memory once for all heads.  Sequence i brings the rows seq_start[i] …
+// seq_start[i+1]−1 at positions seq_pos0[i] … of slot seq_slot[i] (−1: padding, zeros); max_new is the longest run.
+// Decode steps (max_new = 1) may cut every context into n_split parts, which meet in `partials` (float32,
+// vlrf_attn_latent_mma_scratch_floats) and a second kernel.  C a multiple of 32 up to 512, R a multiple of 16.
+int vlrf_attn_latent_mma_takes(int C, int R, int row_w, int BT, int ld_q);
+long long vlrf_attn_latent_mma_scratch_floats(int n_tokens, int H, int C, int n_split);
+int vlrf_attn_latent_mma_group(int C, int R);
+int vlrf_attn_latent_mma(const void* qp, int ld_q, const void* cache, int row_w, int C, int R, const int* block_table,
+                         int max_blocks, const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
+                         int n_seqs, int max_new, int H, int BT, float scale, int window, int n_split, float* partials,
+                         int* dev_err, cudaStream_t stream);
 
 // ---- routed experts (moe.cu) ---------------------------------------------------------------------------------------
 // z: float32 router logits [T][ld_z] (column E: the logit of a shared expert's gate, if shared_gate).  ids, wts, rank
