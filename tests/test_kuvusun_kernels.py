@@ -40,8 +40,10 @@ def test_rms_norm_in_groups(d, groups):
     close(out, want, 2e-6, "replace")
     base = torch.randn(9, d, generator=g, dtype=torch.float64)
     acc = dev(base, torch.float32)
-    ops.group_rmsnorm(yd, wd, 1e-5, groups, acc, accumulate=True)
+    also = torch.zeros(9, d, dtype=torch.bfloat16, device="cuda")
+    ops.group_rmsnorm(yd, wd, 1e-5, groups, acc, accumulate=True, also=also)
     close(acc, base + want, 2e-6, "accumulate")
+    assert torch.equal(also, acc.to(torch.bfloat16)), "the second output is the rounding of the first"
     rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32, device="cuda")
     half = torch.zeros(4, d, dtype=torch.bfloat16, device="cuda")
     ops.group_rmsnorm(yd, wd, 1e-5, groups, half, rows)
@@ -152,6 +154,48 @@ def test_products_per_group(dt):
             close(out[at:at + n], x[at:at + n].double() @ w[e].double().T, 1e-5, f"group {e}")
         at += n
     assert float((out[P:] - 5.0).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,H,N,K", [(300, 5, 72, 64), (70, 3, 512, 32), (1, 16, 40, 128), (129, 2, 130, 200), (64, 20, 24, 24)])
+def test_products_per_head_on_the_tensor_cores(M, H, N, K):
+    """Shapes that the tcgen05 kernel takes (rows and heads on 16-byte boundaries): heads narrower than the 64 columns
+    a copy brings (the neighbour's columns arrive and must count for nothing), row tiles with tails, column tails."""
+    from vlrf_b200.csrc import library, ops
+    g = torch.Generator().manual_seed(M + K)
+    x = dev(torch.randn(M, H, K, generator=g), torch.bfloat16)
+    w = dev(torch.randn(H, N, K, generator=g) / math.sqrt(K), torch.bfloat16)
+    want = torch.einsum("mhk,hnk->mhn", x.double(), w.double())
+    wide = (N + 15) // 8 * 8                                   # heads' outputs inside wider rows, on 16-byte boundaries
+    assert library().vlrf_gemm_tcgen05_groups_takes(M, H, N, K, H * K, K, H * wide, wide, 0)
+    for odt, t in ((torch.bfloat16, 1.2e-2), (torch.float32, 1e-5)):
+        out = torch.full((M, H, wide), 7.0, dtype=odt, device="cuda")
+        ops.linear_heads(x, w, out[:, :, :N], M)
+        close(out[:, :, :N], want, t, f"heads, {odt}")
+        assert float((out[:, :, N:].float() - 7.0).abs().max()) == 0.0, "columns outside the heads' outputs were written"
+    assert ops.device_errors() == 0
+
+
+@pytest.mark.parametrize("counts,N,K", [([0, 5, 130, 0, 64, 1, 0, 300], 200, 96), ([128, 128], 48, 64), ([0, 0, 3], 136, 256),
+                                        ([7] * 40, 64, 32)])
+def test_products_per_group_on_the_tensor_cores(counts, N, K):
+    from vlrf_b200.csrc import library, ops
+    g = torch.Generator().manual_seed(N + K)
+    G, P = len(counts), sum(counts)
+    x = dev(torch.randn(P + 9, K, generator=g), torch.bfloat16)
+    x[P:] = float("nan")                                       # rows of no group are read but must count for nothing
+    w = dev(torch.randn(G, N, K, generator=g) / math.sqrt(K), torch.bfloat16)
+    offsets = torch.tensor([sum(counts[:i]) for i in range(G + 1)], dtype=torch.int32, device="cuda")
+    assert library().vlrf_gemm_tcgen05_groups_takes(P + 9, G, N, K, K, 0, N, 0, 1)
+    for odt, t in ((torch.float32, 1e-5), (torch.bfloat16, 1.2e-2)):
+        out = torch.full((P + 9, N), 5.0, dtype=odt, device="cuda")
+        ops.linear_grouped(x, w, out, offsets, P + 9)
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                close(out[at:at + n], x[at:at + n].double() @ w[e].double().T, t, f"group {e}, {odt}")
+            at += n
+        assert float((out[P:].float() - 5.0).abs().max()) == 0.0
+    assert ops.device_errors() == 0
 
 
 def test_router_chooses_weighs_and_sorts():

@@ -54,6 +54,9 @@ _SIGNATURES = {
     "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_gemm_tcgen05_groups_takes": [_c_int] * 9,
+    "vlrf_gemm_tcgen05_groups": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_prefill_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_attn_prefill": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
@@ -86,7 +89,7 @@ _SIGNATURES = {
                                  _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_decode_program_run": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_group_rmsnorm": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_float, _c_int, _c_void_p],
+                           _c_float, _c_int, _c_void_p, _c_void_p],
     "vlrf_cast_rows": [_c_void_p, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
     "vlrf_gate_mul": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "vlrf_gemm_heads": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,

@@ -135,15 +135,30 @@ attn_latent_mma_kernel(const __nv_bfloat16* __restrict__ qp, int ld_q, const __n
         const bool tile_live = active && key0 <= my_pos && key0 + LM_KT > my_first;
         if (tile_live) {
             // scores of the 16 heads against rows 8w … 8w+7
-            float sc[4] = {0.f, 0.f, 0.f, 0.f};
+            // (four sums side by side: one chain of dependent MMAs over all of k would wait for each one's latency)
+            float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc1[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f}, sc3[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t a_addr = q_base + (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + 8 * (lane >> 4)) * 2;
             const uint32_t b_addr = smem_u32(kt) + (uint32_t)((8 * w + (lane & 7)) * ldk + 8 * ((lane >> 3) & 1)) * 2;
-            for (int kk = 0; kk < D; kk += 16) {
+            int kk = 0;
+            for (; kk + 64 <= D; kk += 64) {
+                uint32_t a0[4], a1[4], a2[4], a3[4], b[8];
+                ldsm_x4(a0, a_addr + kk * 2);        ldsm_x2(b[0], b[1], b_addr + kk * 2);
+                ldsm_x4(a1, a_addr + (kk + 16) * 2); ldsm_x2(b[2], b[3], b_addr + (kk + 16) * 2);
+                ldsm_x4(a2, a_addr + (kk + 32) * 2); ldsm_x2(b[4], b[5], b_addr + (kk + 32) * 2);
+                ldsm_x4(a3, a_addr + (kk + 48) * 2); ldsm_x2(b[6], b[7], b_addr + (kk + 48) * 2);
+                mma_16816(sc, a0, b[0], b[1]);
+                mma_16816(sc1, a1, b[2], b[3]);
+                mma_16816(sc2, a2, b[4], b[5]);
+                mma_16816(sc3, a3, b[6], b[7]);
+            }
+            for (; kk < D; kk += 16) {
                 uint32_t a[4], b0, b1;
                 ldsm_x4(a, a_addr + kk * 2);
                 ldsm_x2(b0, b1, b_addr + kk * 2);
                 mma_16816(sc, a, b0, b1);
             }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[e] = (sc[e] + sc1[e]) + (sc2[e] + sc3[e]);
             const int kcol = key0 + 8 * w + 2 * t4;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {

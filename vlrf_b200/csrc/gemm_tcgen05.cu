@@ -54,6 +54,17 @@ struct TcKvScatter {
     int max_blocks, k_off, v_off, width, dh, Hkv, BT;   // width = Hkv*dh
 };
 
+// Products with a weight matrix per group (GR): group g multiplies rows r0_g … r1_g−1 of X, read at column g·x_gs, by
+// W[g] (rows g·N … of the stacked matrix that tmap_w describes) into the same rows of Y at column g·y_gs.  With
+// `offsets` (device, G + 1 entries) the groups are consecutive row ranges (experts over rows sorted by expert); without,
+// every group takes all `rows` rows (heads, each with columns of its own).  The row tiles of all groups are listed in
+// shared memory once the kernel ahead has finished (it wrote the offsets); a tile never spans two groups, rows beyond
+// its group's end are computed and not stored, and columns of W beyond N (the next group's rows) likewise.
+constexpr int TC_GR_TAB = 512;       // row tiles of all groups together
+struct TcGroups {
+    const int* offsets; int G, x_gs, y_gs, rows;
+};
+
 // SWAP: the roles of the two matrices are exchanged — the 128-row operand is W (tmap_x then describes W),
 // the BN-row operand is X with its few rows — so that a product with few rows still fills the 128-row MMA.
 // The accumulator then holds Yᵀ: lane = output column n, TMEM column = row m; the epilogue writes Y[m][n],
@@ -62,11 +73,14 @@ struct TcKvScatter {
 // The CTA is persistent: it takes the output tiles blockIdx.x, + gridDim.x, …  Tensor memory holds two
 // accumulators, so the epilogue of one tile runs while the MMAs of the next fill the other, and the
 // producer keeps the shared-memory ring full across tile boundaries.
-template <int BN, int STAGES, typename OT, bool SWAP>
+template <int BN, int STAGES, typename OT, bool SWAP, bool GR = false>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const float* __restrict__ bias, const float* residual, OT* Y, int M, int N, int K, int ldy,
-                    int act, TcKvScatter kv, int* __restrict__ dev_err, long long* trace) {
+                    int act, TcKvScatter kv, int* __restrict__ dev_err, long long* trace, TcGroups gr = TcGroups{}) {
+    static_assert(!(GR && SWAP), "groups keep the roles of the operands");
+    __shared__ int gr_m0[GR ? TC_GR_TAB : 1], gr_end[GR ? TC_GR_TAB : 1], gr_g[GR ? TC_GR_TAB : 1];
+    __shared__ int gr_count;
     extern __shared__ unsigned char tc_raw[];
     // (stations of the time stamps, kind 3: 0 the CTA begins, 1 the kernel ahead has finished, 2 the first tile's
     // accumulator is complete, 3 the last tile's, 6 the last tile is stored; thread 0 stamps)
@@ -92,7 +106,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // tiles: not swapped — 128 rows of X by BN rows of W, neighbours in N first (they share the rows of X in
     // L2); swapped — 128 rows of W by all rows of X
     const int tiles_n = SWAP ? 1 : (N + BN - 1) / BN;
-    const int n_tiles = SWAP ? (N + TC_BM - 1) / TC_BM : tiles_n * ((M + TC_BM - 1) / TC_BM);
+    int n_tiles = SWAP ? (N + TC_BM - 1) / TC_BM : tiles_n * ((M + TC_BM - 1) / TC_BM);
+    if (GR) n_tiles = 0;                                            // known once the groups' rows are (below)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], 1); }
@@ -129,12 +144,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     pdl_launch_dependents();
     pdl_wait();                                    // X (and the residual) come from the kernel before
     if (threadIdx.x == 0) VLRF_TRACE(trace, 3, (int)blockIdx.x, 1);
+    if (GR) {
+        if (threadIdx.x == 0) {
+            int n = 0;
+            for (int g = 0; g < gr.G; ++g) {
+                const int lo = gr.offsets ? gr.offsets[g] : 0, hi = gr.offsets ? gr.offsets[g + 1] : gr.rows;
+                for (int r = lo; r < hi && n < TC_GR_TAB; r += TC_BM) { gr_m0[n] = r; gr_end[n] = hi; gr_g[n] = g; ++n; }
+            }
+            gr_count = n;
+        }
+        __syncthreads();
+        n_tiles = tiles_n * gr_count;
+    }
 
     if (warp == 8) {
         if (lane == 0) {
             uint32_t kc = 0;                       // k-blocks requested so far, over all tiles
             for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)s_abort; tile += gridDim.x) {
-                const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+                const int m0 = GR ? gr_m0[tile / tiles_n] : (SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM);
+                const int xk0 = GR ? gr_g[tile / tiles_n] * gr.x_gs : 0;                    // the group's columns of X
+                const int n0 = (SWAP ? 0 : (tile % tiles_n) * BN) + (GR ? gr_g[tile / tiles_n] * N : 0);   // rows of the stacked W
                 for (int kb = 0; kb < n_kb; ++kb, ++kc) {
                     const int s = kc % STAGES;
                     const uint32_t use = kc / STAGES;
@@ -150,7 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     tbar_expect_tx(&full[s], A_BYTES + B_BYTES);
 #pragma unroll
                     for (int a = 0; a < KA; ++a) {
-                        tma_load_2d(a_tiles + (size_t)s * A_BYTES + a * A_ATOM, &tmap_x, (kb * KA + a) * TC_BK, m0, &full[s]);
+                        tma_load_2d(a_tiles + (size_t)s * A_BYTES + a * A_ATOM, &tmap_x, xk0 + (kb * KA + a) * TC_BK, m0, &full[s]);
                         tma_load_2d(b_tiles + (size_t)s * B_BYTES + a * B_ATOM, &tmap_w, (kb * KA + a) * TC_BK, n0, &full[s]);
                     }
                 }
@@ -191,7 +220,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         uint32_t tc = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tc) {
             const uint32_t b = tc & 1;
-            const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+            const int m0 = GR ? gr_m0[tile / tiles_n] : (SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM);
+            const int n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+            const int m_lim = GR ? gr_end[tile / tiles_n] : M;     // rows of the tile beyond it are not stored
+            OT* const Yt = GR ? Y + (size_t)gr_g[tile / tiles_n] * gr.y_gs : Y;
             const int m = m0 + q * 32 + lane;                 // this thread's row (when the roles are not exchanged)
             // where this thread's row goes in the cache, if the product feeds one: three loads, each waiting for
             // the one before, so they go out while the MMAs still run
@@ -253,17 +285,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             constexpr int SPLIT_AT = ((BN / 32 + 1) / 2) * 32;
             const int c_begin = half ? SPLIT_AT : 0, c_end = half ? BN : SPLIT_AT;
             // whether rows of Y, and heads in the cache, lie so that 32-byte stores are aligned
-            const bool wide = (reinterpret_cast<uintptr_t>(Y) & 31) == 0 && (ldy % (32 / (int)sizeof(OT))) == 0;
+            const bool wide = (reinterpret_cast<uintptr_t>(Yt) & 31) == 0 && (ldy % (32 / (int)sizeof(OT))) == 0;
             const bool kv_wide = kv.Kc != nullptr && kv.dh % 16 == 0 && kv.k_off % 16 == 0 && kv.v_off % 16 == 0 &&
                                  ((reinterpret_cast<uintptr_t>(kv.Kc) | reinterpret_cast<uintptr_t>(kv.Vc)) & 31) == 0;
 #pragma unroll 1
             for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_d + (uint32_t)c0, r);          // in flight while the bias and the residual are fetched
-                const bool live = m < M && n0 + c0 < N;
+                const bool live = m < m_lim && n0 + c0 < N;
                 const int n_here = live ? min(32, N - (n0 + c0)) : 0;
                 const bool fast = n_here == 32 && (ldy % 8) == 0;
-                OT* __restrict__ yrow = Y + (size_t)m * ldy + n0 + c0;
+                OT* __restrict__ yrow = Yt + (size_t)m * ldy + n0 + c0;
                 float4 bq[8], rq[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { bq[i] = make_float4(0.f, 0.f, 0.f, 0.f); rq[i] = bq[i]; }
@@ -417,7 +449,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
     const int sms = sm_count_cached();
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // persistent: one CTA per SM at most
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, bias, residual, (OT*)Y, M, N, K, ldy,
-                                   act, kv, dev_err, vlrf_trace_buffer());
+                                   act, kv, dev_err, vlrf_trace_buffer(), TcGroups{});
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_tcgen05");
 }
@@ -496,3 +528,60 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
 #undef TILED
 }
 
+// ---- a weight matrix per group: experts over rows sorted by expert, or heads with columns of their own --------------
+namespace {
+template <int BN, int STAGES, typename OT>
+int launch_tc_groups(const void* X, int ldx, const void* W, void* Y, int ldy, const TcGroups& gr, int N, int K, int* dev_err,
+                     cudaStream_t stream) {
+    CUtensorMap tx, tw;
+    const long long x_cols = gr.offsets ? K : (long long)(gr.G - 1) * gr.x_gs + K;
+    int st = vlrf_make_tmap_bf16(X, gr.rows, x_cols, ldx, TC_BM, TC_BK, &tx);
+    if (st != VLRF_OK) return st;
+    st = vlrf_make_tmap_bf16(W, (long long)gr.G * N, K, K, BN, TC_BK, &tw);
+    if (st != VLRF_OK) return st;
+    const size_t smem = 1024 + (size_t)STAGES * tc_atoms(BN) * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, OT, false, true>;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05_groups: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    // row tiles: at most one partly filled tile a group beyond the rows' own
+    const long long row_tiles = gr.offsets ? (gr.rows + TC_BM - 1) / TC_BM + gr.G : (long long)gr.G * ((gr.rows + TC_BM - 1) / TC_BM);
+    const long long tiles = row_tiles * ((N + BN - 1) / BN);
+    const int sms = sm_count_cached();
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+    cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, (const float*)nullptr, (const float*)nullptr,
+                                   (OT*)Y, gr.rows, N, K, ldy, (int)VLRF_ACT_NONE, TcKvScatter{}, dev_err, vlrf_trace_buffer(), gr);
+    if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05_groups: %s", cudaGetErrorString(e));
+    return vlrf_check_launch("gemm_tcgen05_groups");
+}
+}  // namespace
+
+// Whether the grouped form takes the shape: bfloat16 operands whose rows, groups' columns and results start on
+// 16-byte boundaries, and no more row tiles than its table holds.
+extern "C" int vlrf_gemm_tcgen05_groups_takes(int rows, int G, int N, int K, int ldx, int x_gs, int ldy, int y_gs, int by_offsets) {
+    if (rows < 1 || G < 1 || N < 1 || K < 8 || K % 8 != 0 || ldx % 8 != 0 || x_gs % 8 != 0 || y_gs % 8 != 0 || ldy % 8 != 0) return 0;
+    const long long row_tiles = by_offsets ? (rows + TC_BM - 1) / TC_BM + G : (long long)G * ((rows + TC_BM - 1) / TC_BM);
+    return row_tiles <= TC_GR_TAB ? 1 : 0;
+}
+
+// offsets != null: rows offsets[g] … offsets[g+1]−1 of X [rows][K] times W[g]ᵀ into the same rows of Y [rows][N]
+// (x_gs = y_gs = 0).  offsets == null: every group (head) multiplies all rows, reading X at column g·x_gs and writing Y at
+// column g·y_gs.  W [G][N][K]; X and W bfloat16, Y bfloat16 or float32; no bias, activation or residual.
+extern "C" int vlrf_gemm_tcgen05_groups(const void* X, int ldx, int x_gs, const void* W, void* Y, int ldy, int y_gs,
+                                        const int* offsets, int G, int rows, int N, int K, int out_dtype, int* dev_err,
+                                        cudaStream_t stream) {
+    VLRF_REQUIRE(vlrf_gemm_tcgen05_groups_takes(rows, G, N, K, ldx, x_gs, ldy, y_gs, offsets != nullptr),
+                 "gemm_tcgen05_groups: does not take rows=%d G=%d N=%d K=%d ldx=%d x_gs=%d ldy=%d y_gs=%d", rows, G, N, K, ldx, x_gs, ldy, y_gs);
+    VLRF_REQUIRE(dev_err != nullptr && (out_dtype == VLRF_BF16 || out_dtype == VLRF_F32), "gemm_tcgen05_groups: bad arguments");
+    VLRF_REQUIRE((reinterpret_cast<uintptr_t>(Y) & 15) == 0, "gemm_tcgen05_groups: Y must start on a 16-byte boundary");
+    const TcGroups gr{offsets, G, x_gs, y_gs, rows};
+    if (N <= 64) {
+        return out_dtype == VLRF_BF16 ? launch_tc_groups<64, 4, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream)
+                                      : launch_tc_groups<64, 4, float>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream);
+    }
+    return out_dtype == VLRF_BF16 ? launch_tc_groups<128, 3, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream)
+                                  : launch_tc_groups<128, 3, float>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream);
+}

@@ -5,7 +5,9 @@
 // RMS norm.  The input rows are float32 (a product's float32 result, or the residual stream); sums and the division
 // are float32.  The result either replaces the output row (any dtype) or is added to it (float32: the residual
 // stream, for blocks that norm a sublayer's output before the sum).  `rows` gathers input rows (the rows whose
-// logits are wanted).  The output may be the input: a thread rewrites only elements it has read itself.
+// logits are wanted).  The output may be the input: a thread rewrites only elements it has read itself.  `also`: a
+// second, bfloat16 copy of the finished rows [n_rows][d], which spares the cast of the residual stream that the next
+// sublayer would need.
 //
 // cast_rows: float32 rows to the activation dtype (what a sublayer reads of the float32 residual stream).
 // gate_mul: out = act(a) · b element by element (act: x·sigmoid(x) for gated feed-forwards, sigmoid(x) for gates on
@@ -19,7 +21,7 @@ constexpr int NORM_MAX_GROUPS = 256;
 template <typename OT, bool ACC>
 __global__ void __launch_bounds__(NORM_THREADS)
 group_rmsnorm_kernel(const float* y, int ld_y, const int* __restrict__ rows, const float* __restrict__ w, OT* out,
-                     int ld_out, int d, int groups, float eps) {
+                     int ld_out, int d, int groups, float eps, __nv_bfloat16* also) {
     __shared__ float inv_sm[NORM_MAX_GROUPS];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -38,6 +40,7 @@ group_rmsnorm_kernel(const float* y, int ld_y, const int* __restrict__ rows, con
         float v = yr[i] * inv_sm[i / gs] * w[i];
         if (ACC) v += ElemIO<OT>::load(o + i);
         ElemIO<OT>::store(o + i, v);
+        if (also != nullptr) also[(size_t)r * d + i] = __float2bfloat16_rn(v);     // what the next sublayer reads of the row
     }
 }
 
@@ -53,6 +56,26 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, OT* __restrict__ o
     }
 }
 
+// the same, eight bfloat16 a thread (rows and columns on 16-byte boundaries)
+__global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __nv_bfloat16* b, int ldb, __nv_bfloat16* out, int ldo,
+                                       int rows, int cols8, int act) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols8) return;
+    const int r = (int)(i / cols8), c = (int)(i - (long long)r * cols8) * 8;
+    const uint4 ga = *reinterpret_cast<const uint4*>(a + (size_t)r * lda + c), va = *reinterpret_cast<const uint4*>(b + (size_t)r * ldb + c);
+    const uint32_t gw[4] = {ga.x, ga.y, ga.z, ga.w}, vw[4] = {va.x, va.y, va.z, va.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+        const float v0 = __uint_as_float(vw[k] << 16), v1 = __uint_as_float(vw[k] & 0xffff0000u);
+        const float f0 = act == VLRF_ACT_SILU ? silu_f(g0) : sigmoid_f(g0), f1 = act == VLRF_ACT_SILU ? silu_f(g1) : sigmoid_f(g1);
+        const __nv_bfloat162 p = __floats2bfloat162_rn(f0 * v0, f1 * v1);
+        o[k] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <typename ET>
 __global__ void gate_mul_kernel(const ET* a, int lda, const ET* b, int ldb, ET* out, int ldo, int rows, int cols, int act) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -66,7 +89,7 @@ __global__ void gate_mul_kernel(const ET* a, int lda, const ET* b, int ldb, ET* 
 }  // namespace
 
 extern "C" int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w, void* out, int out_dtype,
-                                  int ld_out, int n_rows, int d, int groups, float eps, int accumulate,
+                                  int ld_out, int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16,
                                   cudaStream_t stream) {
     VLRF_REQUIRE(n_rows >= 0 && d > 0 && groups > 0 && groups <= NORM_MAX_GROUPS, "group_rmsnorm: bad sizes rows=%d d=%d groups=%d", n_rows, d, groups);
     VLRF_REQUIRE(d % groups == 0, "group_rmsnorm: %d columns cannot be cut into %d equal parts", d, groups);
@@ -74,10 +97,10 @@ extern "C" int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, con
     VLRF_REQUIRE(!accumulate || out_dtype == VLRF_F32, "group_rmsnorm: only float32 rows can be added to");
     if (n_rows == 0) return VLRF_OK;
     if (out_dtype == VLRF_F32) {
-        if (accumulate) group_rmsnorm_kernel<float, true><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps);
-        else group_rmsnorm_kernel<float, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps);
+        if (accumulate) group_rmsnorm_kernel<float, true><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
+        else group_rmsnorm_kernel<float, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
     } else if (out_dtype == VLRF_BF16) {
-        group_rmsnorm_kernel<__nv_bfloat16, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (__nv_bfloat16*)out, ld_out, d, groups, eps);
+        group_rmsnorm_kernel<__nv_bfloat16, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (__nv_bfloat16*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
     } else {
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "group_rmsnorm: unknown output dtype %d", out_dtype);
     }
@@ -101,7 +124,13 @@ extern "C" int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, voi
     if (rows == 0) return VLRF_OK;
     const long long n = (long long)rows * cols;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == VLRF_BF16)
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                         cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
+    if (dtype == VLRF_BF16 && aligned) {
+        const long long n8 = n / 8;
+        gate_mul_bf16x8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb,
+                                                                               (__nv_bfloat16*)out, ldo, rows, cols / 8, act);
+    } else if (dtype == VLRF_BF16)
         gate_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, rows, cols, act);
     else if (dtype == VLRF_F32)
         gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, rows, cols, act);

@@ -544,10 +544,11 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
 
 # ---- RMS norm in groups, casts, gates ------------------------------------------------------------------------------
 
-def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate: bool = False, n_rows: int | None = None) -> None:
+def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate: bool = False, n_rows: int | None = None,
+                  also=None) -> None:
     """out[r] (+)= y[rows[r] if rows is given else r] normed in `groups` equal consecutive parts (each divided by
     sqrt(mean(part²) + eps)) and multiplied by weight.  y float32; out float32 or bfloat16 (adding: float32 only).
-    out may be y itself."""
+    out may be y itself.  `also`: a bfloat16 tensor [rows, d] that receives the finished rows as well."""
     _dev(y, "y", torch.float32); _dev(weight, "weight", torch.float32); _dev(out, "out")
     d = y.shape[1]
     n = y.shape[0] if n_rows is None else n_rows
@@ -556,8 +557,12 @@ def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate
         n = rows.shape[0]
     if weight.shape[0] != d or out.shape[1] != d or out.shape[0] < n:
         raise KernelError("group_rmsnorm: sizes do not match")
+    if also is not None:
+        _dev(also, "also", torch.bfloat16)
+        if also.shape[1] != d or also.shape[0] < n:
+            raise KernelError("group_rmsnorm: the second output does not match")
     call("vlrf_group_rmsnorm", _ptr(y), d, _ptr(rows), _ptr(weight), _ptr(out), dtype_code(out.dtype), d, n, d, int(groups),
-         float(eps), 1 if accumulate else 0, _stream())
+         float(eps), 1 if accumulate else 0, _ptr(also), _stream())
 
 
 def cast_rows(x, out, n_rows: int) -> None:
@@ -579,6 +584,9 @@ def gate_mul(a, b, out, gate: str, n_rows: int, cols: int) -> None:
 
 
 # ---- products per head and per group ---------------------------------------------------------------------------------
+#: bfloat16 products per head and per group on the tcgen05 kernel where it takes the shape (off: the CUDA cores' kernels)
+GROUPED_TCGEN05 = True
+
 
 def linear_heads(x, w, out, n_rows: int) -> None:
     """out[m, h, :] = x[m, h, :] · w[h]ᵀ for every head.  x [M, H, K] and out [M, H, N] may be views into wider rows
@@ -590,6 +598,12 @@ def linear_heads(x, w, out, n_rows: int) -> None:
             raise KernelError(f"linear_heads: {name} {list(t.shape)} does not match w {list(w.shape)}")
     if out.dtype not in (torch.float32, x.dtype):
         raise KernelError("linear_heads: the result is float32 or of the operands' dtype")
+    if x.dtype == torch.bfloat16 and USE_TCGEN05 and GROUPED_TCGEN05 and x.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0:
+        from . import library
+        if library().vlrf_gemm_tcgen05_groups_takes(n_rows, H, N, K, x.stride(0), x.stride(1), out.stride(0), out.stride(1), 0):
+            call("vlrf_gemm_tcgen05_groups", _ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1),
+                 0, H, n_rows, N, K, dtype_code(out.dtype), _ptr(_dev_err()), _stream())
+            return
     call("vlrf_gemm_heads", _ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1), n_rows, N, K,
          H, dtype_code(x.dtype), dtype_code(out.dtype), _stream())
 
@@ -601,6 +615,12 @@ def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
     G, N, K = w.shape
     if x.shape[1] != K or out.shape[1] != N or min(x.shape[0], out.shape[0]) < n_rows or offsets.numel() < G + 1:
         raise KernelError("linear_grouped: sizes do not match")
+    if x.dtype == torch.bfloat16 and USE_TCGEN05 and GROUPED_TCGEN05 and n_rows > 0:
+        from . import library
+        if library().vlrf_gemm_tcgen05_groups_takes(n_rows, G, N, K, K, 0, N, 0, 1):
+            call("vlrf_gemm_tcgen05_groups", _ptr(x), K, 0, _ptr(w), _ptr(out), N, 0, _ptr(offsets), G, n_rows, N, K,
+                 dtype_code(out.dtype), _ptr(_dev_err()), _stream())
+            return
     call("vlrf_gemm_grouped", _ptr(x), _ptr(w), _ptr(out), _ptr(offsets), G, n_rows, N, K, dtype_code(x.dtype),
          dtype_code(out.dtype), _stream())
 

@@ -88,6 +88,13 @@ int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias, const flo
                       int ldx, int ldy, int out_dtype, int act, void* Kc, void* Vc, const int* block_table,
                       int max_blocks, const int* tok_slot, const int* tok_pos, int k_off, int v_off, int Hkv, int dh,
                       int BT, int* dev_err, cudaStream_t stream);
+// The same kernel with a weight matrix per group.  offsets != null (device, G + 1 entries): rows offsets[g] …
+// offsets[g+1]−1 of X [rows][K] times W[g]ᵀ into the same rows of Y [rows][N] (experts over rows sorted by expert;
+// x_gs = y_gs = 0).  offsets == null: every group multiplies all rows, reading X at column g·x_gs and writing Y at
+// column g·y_gs (heads).  W [G][N][K]; no bias, activation, residual or scatter.
+int vlrf_gemm_tcgen05_groups_takes(int rows, int G, int N, int K, int ldx, int x_gs, int ldy, int y_gs, int by_offsets);
+int vlrf_gemm_tcgen05_groups(const void* X, int ldx, int x_gs, const void* W, void* Y, int ldy, int y_gs, const int* offsets,
+                             int G, int rows, int N, int K, int out_dtype, int* dev_err, cudaStream_t stream);
 // For measurements: force the tile width (64 … 256 in steps of 32), 0 = chosen by size again.
 int vlrf_gemm_tcgen05_force_width(int bn);
 
@@ -173,8 +180,9 @@ int vlrf_attn_decode_noalloc(const void* qkv, int dtype, int ld, int q_off, cons
 // into `groups` equal consecutive parts with a root mean square each (groups = 1: the plain RMS norm).  y float32 of
 // row stride ld_y; out of out_dtype and row stride ld_out; accumulate (float32 out only) adds to the row instead of
 // replacing it.  out may be y.
+// also_bf16 (or null): the finished rows once more, as bfloat16 [n_rows][d].
 int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w, void* out, int out_dtype, int ld_out,
-                       int n_rows, int d, int groups, float eps, int accumulate, cudaStream_t stream);
+                       int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16, cudaStream_t stream);
 // n float32 numbers to out_dtype.
 int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
 // out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU or VLRF_ACT_SIGMOID, all three of `dtype` with row strides of

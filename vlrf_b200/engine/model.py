@@ -127,6 +127,7 @@ class DecoderModel:
         (reference: include/model/transformer.hpp:335-424, which keeps the last row only)."""
         x = ctx.ws.get("residual", ctx.n_tokens, self.width, torch.float32)
         ctx.ws.row_stats.forget()                      # nothing is known about the rows of the step before
+        ctx.ws.input_cast = None
         self.embedding(ctx, x)
         if not getattr(self.embedding, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
@@ -136,6 +137,8 @@ class DecoderModel:
             self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
             if not getattr(self.layers[call.layer], "leaves_row_stats", False):
                 ctx.ws.row_stats.forget()              # a block of another kind that does not vouch for them
+            if not getattr(self.layers[call.layer], "leaves_input_cast", False):
+                ctx.ws.input_cast = None               # (a rounding of the rows that a block of that kind left: stale now)
         n = ctx.n_logit_rows
         logits = ctx.ws.get("logits", max(n, 1), self.vocab_size, torch.float32)
         if n == 0:

@@ -67,20 +67,35 @@ class SublayerNormBlock:
     def cache_need(self):
         return self.mixer.cache_need() if self.mixer is not None else None
 
+    #: the block leaves `ws.input_cast` true (see `_input`); the model forgets it after layers that do not say so
+    leaves_input_cast = True
+
     def _input(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """What a sublayer reads: x itself in the 32-bit engine, else its rounding to the activation dtype.  The norm
+        that last added to x has written that rounding already (`ws.input_cast` names the rows it is of); only the
+        first sublayer after something else wrote x (the embedding) casts."""
         if ctx.act_dtype == torch.float32:
             return x
         from ..csrc import ops
         h = ctx.ws.get("block_input", ctx.n_tokens, x.shape[1], ctx.act_dtype)
-        ops.cast_rows(x, h, ctx.n_tokens)
+        if getattr(ctx.ws, "input_cast", None) != (x.data_ptr(), ctx.n_tokens, id(ctx)):
+            ops.cast_rows(x, h, ctx.n_tokens)
         return h
+
+    def _add_normed(self, norm, y, x, ctx: StepContext) -> None:
+        if ctx.act_dtype == torch.bfloat16 and hasattr(norm, "groups"):
+            norm(y, x, accumulate=True, also=ctx.ws.get("block_input", ctx.n_tokens, x.shape[1], ctx.act_dtype))
+            ctx.ws.input_cast = (x.data_ptr(), ctx.n_tokens, id(ctx))
+        else:
+            norm(y, x, accumulate=True)
+            ctx.ws.input_cast = None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
         ctx.ws.row_stats.forget()
         y = ctx.ws.get("block_sublayer_out", ctx.n_tokens, x.shape[1], torch.float32)
         if self.mixer is not None:
             self.mixer.forward(self._input(x, ctx), y, ctx, view, writes_cache, accumulate=False)
-            self.norm1(y, x, accumulate=True)
+            self._add_normed(self.norm1, y, x, ctx)
         if self.feed_forward is not None:
             self.feed_forward.forward(self._input(x, ctx), y, ctx, accumulate=False)
-            self.norm2(y, x, accumulate=True)
+            self._add_normed(self.norm2, y, x, ctx)

@@ -27,6 +27,9 @@ class Workspace:
         #: statistics of the residual rows that the step's last product wrote (see csrc.ops.RowStats); parts hand
         #: this to the products that may leave or use them, the block forgets them after parts it cannot vouch for
         self.row_stats = RowStats(self.device)
+        #: (address, rows, step) of the float32 rows whose rounding to the activation dtype lies in "block_input", or
+        #: None: written by blocks whose norm leaves that rounding, forgotten by the model after every other layer
+        self.input_cast = None
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, rows, cols, dtype)

@@ -41,6 +41,8 @@ class GroupRMSNorm:
         self.weight, self.eps, self.groups = weight, float(eps), int(groups)
         self.width = weight.shape[0]
 
-    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
-        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows, accumulate)
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, accumulate: bool = False,
+                 also: torch.Tensor | None = None) -> torch.Tensor:
+        """also: a bfloat16 tensor that receives the finished rows as well (what the next sublayer reads of them)."""
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows, accumulate, also=also)
         return out
