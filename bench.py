@@ -408,6 +408,126 @@ def design_point(model_dir: str, prompt_len: int, batches, steps: int, warmup: i
     return out
 
 
+def design_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
+    """The design's own kernels alone, each beside the like kernel of GPT-2 at equal size: 20 launches back to back
+    between two events after 3 warm-up launches, inputs rotated over buffers that together exceed L2 where a kernel is
+    bound by bytes.  Fractions are of the measured copy bandwidth or bf16 product throughput."""
+    import types
+    import torch
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.parts.context import Workspace
+    dev, bf = "cuda", torch.bfloat16
+    H, C, R, dim, vdim, width = z["heads"], z["kv_rank"], z["rot"], z["dim"], z["vdim"], z["width"]
+    D = C + R
+    dev_err = torch.zeros(1, dtype=torch.int32, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def timed(fn, reps=20):
+        for i in range(3):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3           # microseconds a launch
+
+    out = {}
+    # -- decode attention: 64 sequences at context 1,024 ----------------------------------------------------------------
+    B, ctxlen = 64, 1024
+    nblk = B * ctxlen // 64
+    table = torch.arange(nblk, dtype=torch.int32, device=dev).view(B, ctxlen // 64).contiguous()
+    slots, pos = i32(list(range(B))), i32([ctxlen - 1] * B)
+    n_buf = max(2, int(300e6 // (nblk * 64 * D * 2)) + 1)
+    caches = [torch.randn(nblk, 64, D, device=dev).to(bf) for _ in range(n_buf)]
+    qp = torch.randn(B, H * D, device=dev).to(bf)
+    o = torch.zeros(B, H * C, dtype=bf, device=dev)
+    ctx = types.SimpleNamespace(max_new=1, n_seqs=B, seq_slot=slots, seq_start=i32(list(range(B + 1))), seq_pos0=pos,
+                                max_context=ctxlen, ws=Workspace(dev))
+    us = timed(lambda i: ops.attention_latent(qp, caches[i % n_buf], C, R, table, slots, pos, o, B, H, 0.1, 0, dev_err, ctx=ctx))
+    nbytes = B * ctxlen * D * 2
+    out["attention_decode"] = {"kuvusun": {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
+                                           "mib": round(nbytes / 2**20, 1)}}
+    del caches
+    dh = width // H
+    n_buf = max(2, int(300e6 // (2 * nblk * H * 64 * dh * 2)) + 1)
+    ks = [torch.randn(nblk, H, 64, dh, device=dev).to(bf) for _ in range(n_buf)]
+    vs = [torch.randn(nblk, H, 64, dh, device=dev).to(bf) for _ in range(n_buf)]
+    qkv = torch.randn(B, 3 * width, device=dev).to(bf)
+    o2 = torch.zeros(B, width, dtype=bf, device=dev)
+    n_split = ops.decode_splits(B, H, ctxlen)
+    ws = Workspace(dev)
+    partials = counters = None
+    if n_split > 1 and ops.attention_decode_needs_scratch(dh, n_split):
+        partials = ws.get("p", B * H * n_split, dh + 2, torch.float32)
+        counters = ws.get_zeroed("c", B * H, torch.int32)
+    us = timed(lambda i: ops.attention_decode(qkv, 0, ks[i % n_buf], vs[i % n_buf], table, slots, pos, o2, B, H, H, dh, 0.1, 0, n_split,
+                                              partials, counters, dev_err))
+    nbytes = 2 * B * ctxlen * H * dh * 2
+    out["attention_decode"]["gpt2"] = {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3),
+                                       "mib": round(nbytes / 2**20, 1)}
+    # -- prompt attention: 2 sequences of 1,024 tokens -----------------------------------------------------------------
+    S, L = 2, 1024
+    T = S * L
+    tok_slot = i32([s for s in range(S) for _ in range(L)])
+    tok_pos = i32(list(range(L)) * S)
+    pctx = types.SimpleNamespace(max_new=L, n_seqs=S, seq_slot=i32(list(range(S))), seq_start=i32([0, L, 2 * L]), seq_pos0=i32([0, 0]),
+                                 max_context=L, ws=Workspace(dev))
+    ptable = torch.arange(S * L // 64, dtype=torch.int32, device=dev).view(S, L // 64).contiguous()
+    cache = torch.randn(S * L // 64, 64, D, device=dev).to(bf)
+    qpp = torch.randn(T, H * D, device=dev).to(bf)
+    op = torch.zeros(T, H * C, dtype=bf, device=dev)
+    us = timed(lambda i: ops.attention_latent(qpp, cache, C, R, ptable, tok_slot, tok_pos, op, T, H, 0.1, 0, dev_err, ctx=pctx), reps=10)
+    pairs = S * L * (L + 1) / 2
+    done = 2.0 * pairs * H * (D + C)                           # what the kernel multiplies (queries carried into latent space)
+    asked = 2.0 * pairs * H * (dim + R + vdim)                 # what the design's equations ask for, keys and values per head
+    out["attention_prompt"] = {"kuvusun": {"us": round(us, 1), "tflops_done": round(done / us / 1e6, 1), "frac_done": round(done / us / 1e6 / bf16_tflops, 3),
+                                           "tflops_asked": round(asked / us / 1e6, 1), "frac_asked": round(asked / us / 1e6 / bf16_tflops, 4)}}
+    k1, v1 = ks[0][:S * L // 64], vs[0][:S * L // 64]
+    qkvp = torch.randn(T, 3 * width, device=dev).to(bf)
+    op2 = torch.zeros(T, width, dtype=bf, device=dev)
+    if ops.attention_prefill_takes(bf, dh, 64, 3 * width, 0):
+        n_parts = ops.attention_prefill_parts(bf, S, L, H, dh, 64, 3 * width, 0)
+        pp = cc = None
+        if n_parts > 1:
+            nf, nc = ops.attention_prefill_scratch(S, L, H, n_parts)
+            pp, cc = ws.get("pp", nf, 1, torch.float32), ws.get_zeroed("pc", nc, torch.int32)
+        us = timed(lambda i: ops.attention_prefill(qkvp, 0, k1, v1, ptable, pctx.seq_slot, pctx.seq_start, pctx.seq_pos0, op2, T, S, L, H, H,
+                                                   dh, 0.1, 0, dev_err, n_parts, pp, cc), reps=10)
+        fl = 4.0 * pairs * H * dh
+        out["attention_prompt"]["gpt2"] = {"us": round(us, 1), "tflops_done": round(fl / us / 1e6, 1), "frac_done": round(fl / us / 1e6 / bf16_tflops, 3)}
+    del ks, vs
+    # -- the experts' first product: prompt step (T · top rows) and decode step (64 · top rows), rows dealt evenly -------
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    w = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
+    for label, rows in (("experts_prompt", T * top), ("experts_decode", 64 * top)):
+        x = torch.randn(rows, width, device=dev).to(bf)
+        y = torch.zeros(rows, 2 * ff, dtype=bf, device=dev)
+        offs = i32([rows * e // E for e in range(E + 1)])
+        us = timed(lambda i: ops.linear_grouped(x, w, y, offs, rows))
+        fl, nbytes = 2.0 * rows * 2 * ff * width, E * 2 * ff * width * 2
+        out[label] = {"kuvusun": {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 3),
+                                  "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3)}}
+    n_w = max(2, int(300e6 // (z["ff"] * width * 2)) + 1)
+    wd = [(torch.randn(z["ff"], width, device=dev) * 0.02).to(bf) for _ in range(n_w)]
+    for label, rows in (("experts_prompt", T), ("experts_decode", 64)):
+        x = torch.randn(rows, width, device=dev).to(bf)
+        y = torch.zeros(rows, z["ff"], dtype=bf, device=dev)
+        us = timed(lambda i: ops.linear(x, wd[i % n_w], None, y))
+        fl, nbytes = 2.0 * rows * z["ff"] * width, z["ff"] * width * 2
+        out[label]["gpt2"] = {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 3),
+                              "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3)}
+    # -- the products per head around the attention (queries into latent space), prompt step --------------------------------
+    qn = torch.randn(T, H, dim, device=dev).to(bf)
+    wk = (torch.randn(H, C, dim, device=dev) * 0.05).to(bf)
+    us = timed(lambda i: ops.linear_heads(qn, wk, qpp.view(T, H, D)[:, :, :C], T))
+    fl = 2.0 * T * H * C * dim
+    out["heads_prompt"] = {"kuvusun": {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 3)}}
+    return out
+
+
 def design_bench(args) -> int:
     """`--design kuvusun`: the design at sizes like a real model's layers (random weights) beside a GPT-2 of equal
     size: prefill and decode throughput, and each kernel's time.  One JSON line."""
@@ -420,9 +540,11 @@ def design_bench(args) -> int:
         z = DESIGN_SIZES[name]
         point = {"sizes": z}
         with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
-            for label, cfg in (("kuvusun", kuvusun_config(z)), ("gpt2", gpt2_config_like(z))):
+            for label, cfg in (() if args.design_only_kernels else (("kuvusun", kuvusun_config(z)), ("gpt2", gpt2_config_like(z)))):
                 d = str(write_random_model(cfg, 1234, os.path.join(tmp, label)))
                 point[label] = design_point(d, args.design_prompt, [8, 64], max(8, min(args.steps, 64)), max(3, min(args.warmup, 8)))
+        if not args.design_no_kernels:
+            point["kernels"] = design_kernels(z, hbm_gbs, bf16_tflops)
         line["sizes"][name] = point
     print(json.dumps(line))
     return 0
@@ -476,6 +598,8 @@ def main() -> int:
     ap.add_argument("--design", default=None, choices=["kuvusun"],
                     help="instead of the default workload: this design at sizes like a real model's layers beside a GPT-2 of equal size")
     ap.add_argument("--design-sizes", default="s,m", help="with --design: which of the sizes %s" % ",".join(DESIGN_SIZES))
+    ap.add_argument("--design-no-kernels", action="store_true", help="with --design: whole steps only, not each kernel alone")
+    ap.add_argument("--design-only-kernels", action="store_true", help="with --design: each kernel alone only")
     ap.add_argument("--design-prompt", type=int, default=1024, help="with --design: tokens of each of the two prompts, and the decode steps' first context")
     args = ap.parse_args()
 

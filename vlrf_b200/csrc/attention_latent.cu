@@ -40,6 +40,8 @@ latent_append_kernel(const float* __restrict__ proj, int ld, int C, int R, const
                      const float* __restrict__ inv_freq, int rot_dims, ET* __restrict__ cache, int row_w,
                      const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                      const int* __restrict__ tok_pos, int BT, int* __restrict__ dev_err) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     __shared__ float part[4];
     const int t = blockIdx.x;
     const int slot = tok_slot[t];
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(128)
 latent_q_rows_kernel(const float* __restrict__ q, int ld_q, int H, int dim, int R, const float* __restrict__ inv_freq,
                      int rot_dims, const int* __restrict__ tok_pos, ET* __restrict__ qn, int ld_qn,
                      ET* __restrict__ qp, int ld_qp, int C) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const float pos = (float)tok_pos[t];
     const float* src = q + (size_t)t * ld_q;
@@ -105,6 +109,8 @@ attn_latent_kernel(const ET* __restrict__ qp, int ld_q, const ET* __restrict__ c
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                    const int* __restrict__ tok_pos, ET* __restrict__ out, int ld_out, int H, int BT, float scale,
                    int window, int* __restrict__ dev_err) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     extern __shared__ float q_sm[];                            // [LAT_WARPS][C + R]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -182,9 +188,9 @@ extern "C" int vlrf_latent_append(const float* proj, int ld, int C, int R, const
     VLRF_REQUIRE(norm_w != nullptr && dev_err != nullptr, "latent_append: needs the norm's weight and the device error word");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        latent_append_kernel<float><<<T, 128, 0, stream>>>(proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (float*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
+        launch_chained(latent_append_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (float*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
     else if (dtype == VLRF_BF16)
-        latent_append_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (__nv_bfloat16*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
+        launch_chained(latent_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (__nv_bfloat16*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_append: unknown dtype %d", dtype);
     return vlrf_check_launch("latent_append");
 }
@@ -197,9 +203,9 @@ extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int 
     VLRF_REQUIRE(rot_dims >= 0 && rot_dims <= R && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq != nullptr), "latent_q_rows: bad rotation");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        latent_q_rows_kernel<float><<<T, 128, 0, stream>>>(q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (float*)qn, ld_qn, (float*)qp, ld_qp, C);
+        launch_chained(latent_q_rows_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (float*)qn, ld_qn, (float*)qp, ld_qp, C);
     else if (dtype == VLRF_BF16)
-        latent_q_rows_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (__nv_bfloat16*)qn, ld_qn, (__nv_bfloat16*)qp, ld_qp, C);
+        launch_chained(latent_q_rows_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (__nv_bfloat16*)qn, ld_qn, (__nv_bfloat16*)qp, ld_qp, C);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_q_rows: unknown dtype %d", dtype);
     return vlrf_check_launch("latent_q_rows");
 }
@@ -217,9 +223,9 @@ extern "C" int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void*
     dim3 grid(T, (H + LAT_WARPS - 1) / LAT_WARPS);
     const size_t smem = (size_t)LAT_WARPS * (C + R) * sizeof(float);
     if (dtype == VLRF_F32)
-        attn_latent_kernel<float><<<grid, LAT_WARPS * 32, smem, stream>>>((const float*)qp, ld_q, (const float*)cache, row_w, C, R, block_table, max_blocks, tok_slot, tok_pos, (float*)out, ld_out, H, BT, scale, window, dev_err);
+        launch_chained(attn_latent_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(smem), stream, (const float*)qp, ld_q, (const float*)cache, row_w, C, R, block_table, max_blocks, tok_slot, tok_pos, (float*)out, ld_out, H, BT, scale, window, dev_err);
     else if (dtype == VLRF_BF16)
-        attn_latent_kernel<__nv_bfloat16><<<grid, LAT_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)qp, ld_q, (const __nv_bfloat16*)cache, row_w, C, R, block_table, max_blocks, tok_slot, tok_pos, (__nv_bfloat16*)out, ld_out, H, BT, scale, window, dev_err);
+        launch_chained(attn_latent_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(smem), stream, (const __nv_bfloat16*)qp, ld_q, (const __nv_bfloat16*)cache, row_w, C, R, block_table, max_blocks, tok_slot, tok_pos, (__nv_bfloat16*)out, ld_out, H, BT, scale, window, dev_err);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "attn_latent: unknown dtype %d", dtype);
     return vlrf_check_launch("attn_latent");
 }

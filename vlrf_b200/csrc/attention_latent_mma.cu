@@ -53,6 +53,8 @@ attn_latent_mma_kernel(const __nv_bfloat16* __restrict__ qp, int ld_q, const __n
                        const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, int tiles_per_seq,
                        __nv_bfloat16* __restrict__ out, int ld_out, int H, int BT, float scale, int window, int n_split,
                        float* __restrict__ partials, int* __restrict__ dev_err) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char lm_raw[];
     const int D = C + R, ldk = D + 8;                              // shared rows padded by 16 bytes: ldmatrix without conflicts
     __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(lm_raw);                     // [G][16][ldk]
@@ -215,13 +217,22 @@ attn_latent_mma_kernel(const __nv_bfloat16* __restrict__ qp, int ld_q, const __n
             const uint32_t v_addr = smem_u32(kt) + (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + w * cw) * 2;
 #pragma unroll
             for (int nt = 0; nt < LM_NT_MAX; ++nt) {
-                if (nt < nt_cnt) {
-                    acc[nt][0] *= corr[0]; acc[nt][1] *= corr[0]; acc[nt][2] *= corr[1]; acc[nt][3] *= corr[1];
+                if (nt < nt_cnt) { acc[nt][0] *= corr[0]; acc[nt][1] *= corr[0]; acc[nt][2] *= corr[1]; acc[nt][3] *= corr[1]; }
+            }
+            // four column tiles at a time: their operands are requested together, then the four MMAs follow, so that
+            // one wait for shared memory covers four of them (the statements keep their order in the program)
+#pragma unroll
+            for (int nt0 = 0; nt0 < LM_NT_MAX; nt0 += 4) {
+                if (nt0 < nt_cnt) {
 #pragma unroll
                     for (int kk = 0; kk < 2; ++kk) {
-                        uint32_t b0, b1;
-                        ldsm_x2_trans(b0, b1, v_addr + (uint32_t)(16 * kk * ldk + nt * 8) * 2);
-                        mma_16816(acc[nt], pa[kk], b0, b1);
+                        uint32_t b[4][2];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (nt0 + i < nt_cnt) ldsm_x2_trans(b[i][0], b[i][1], v_addr + (uint32_t)(16 * kk * ldk + (nt0 + i) * 8) * 2);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (nt0 + i < nt_cnt) mma_16816(acc[nt0 + i], pa[kk], b[i][0], b[i][1]);
                     }
                 }
             }
@@ -264,6 +275,8 @@ attn_latent_mma_kernel(const __nv_bfloat16* __restrict__ qp, int ld_q, const __n
 __global__ void __launch_bounds__(128)
 attn_latent_merge_kernel(const float* __restrict__ partials, const int* __restrict__ tok_slot, __nv_bfloat16* __restrict__ out,
                          int ld_out, int H, int C, int n_split) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const int tok = blockIdx.x, h = blockIdx.y;
     const int hgs = (H + 15) / 16, hg = h >> 4, r = h & 15;
     __nv_bfloat16* dst = out + (size_t)tok * ld_out + (size_t)h * C;
@@ -334,11 +347,11 @@ extern "C" int vlrf_attn_latent_mma(const void* qp, int ld_q, const void* cache,
         if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_latent_mma: shared memory: %s", cudaGetErrorString(e));
         raised[G == 4] = true;
     }
-    kern<<<grid, G * 128, smem, stream>>>((const __nv_bfloat16*)qp, ld_q, (const __nv_bfloat16*)cache, row_w, C, R, block_table,
+    launch_chained(kern, dim3(grid), dim3(G * 128), (size_t)(smem), stream, (const __nv_bfloat16*)qp, ld_q, (const __nv_bfloat16*)cache, row_w, C, R, block_table,
                                           max_blocks, seq_slot, seq_start, seq_pos0, tiles_per_seq, (__nv_bfloat16*)out, ld_out, H,
                                           BT, scale, window, n_split, partials, dev_err);
     int st = vlrf_check_launch("attn_latent_mma");
     if (st != VLRF_OK || n_split == 1) return st;
-    attn_latent_merge_kernel<<<dim3(n_seqs, H), 128, 0, stream>>>(partials, seq_slot, (__nv_bfloat16*)out, ld_out, H, C, n_split);
+    launch_chained(attn_latent_merge_kernel, dim3(dim3(n_seqs, H)), dim3(128), (size_t)(0), stream, partials, seq_slot, (__nv_bfloat16*)out, ld_out, H, C, n_split);
     return vlrf_check_launch("attn_latent_merge");
 }

@@ -66,6 +66,8 @@ template <typename IT, typename OT>
 __global__ void __launch_bounds__(HTHREADS)
 gemm_heads_kernel(const IT* __restrict__ X, int ldx, int x_hs, const IT* __restrict__ W, OT* __restrict__ Y, int ldy,
                   int y_hs, int M, int N, int K) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     __shared__ float As[HBK][HBM + 4];
     __shared__ float Bs[HBK][HBN + 4];
     const int h = blockIdx.z;
@@ -77,6 +79,8 @@ template <typename IT, typename OT>
 __global__ void __launch_bounds__(HTHREADS)
 gemm_grouped_kernel(const IT* __restrict__ X, const IT* __restrict__ W, OT* __restrict__ Y, const int* __restrict__ offsets,
                     int G, int N, int K) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     __shared__ float As[HBK][HBM + 4];
     __shared__ float Bs[HBK][HBN + 4];
     __shared__ int where[3];                                   // group, first row, end of the group's rows
@@ -103,7 +107,7 @@ extern "C" int vlrf_gemm_heads(const void* X, int ldx, int x_hs, const void* W, 
     if (M == 0) return VLRF_OK;
     dim3 grid((N + HBN - 1) / HBN, (M + HBM - 1) / HBM, H);
     VLRF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_heads: too many row tiles or heads");
-#define LAUNCH(IT, OT) gemm_heads_kernel<IT, OT><<<grid, HTHREADS, 0, stream>>>((const IT*)X, ldx, x_hs, (const IT*)W, (OT*)Y, ldy, y_hs, M, N, K)
+#define LAUNCH(IT, OT) launch_chained(gemm_heads_kernel<IT, OT>, dim3(grid), dim3(HTHREADS), (size_t)(0), stream, (const IT*)X, ldx, x_hs, (const IT*)W, (OT*)Y, ldy, y_hs, M, N, K)
     if (in_dtype == VLRF_F32 && out_dtype == VLRF_F32) LAUNCH(float, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_F32) LAUNCH(__nv_bfloat16, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -118,7 +122,7 @@ extern "C" int vlrf_gemm_grouped(const void* X, const void* W, void* Y, const in
     if (P == 0) return VLRF_OK;
     dim3 grid((N + HBN - 1) / HBN, (P + HBM - 1) / HBM + G);
     VLRF_REQUIRE(grid.y <= 65535, "gemm_grouped: too many row tiles");
-#define LAUNCH(IT, OT) gemm_grouped_kernel<IT, OT><<<grid, HTHREADS, 0, stream>>>((const IT*)X, (const IT*)W, (OT*)Y, offsets, G, N, K)
+#define LAUNCH(IT, OT) launch_chained(gemm_grouped_kernel<IT, OT>, dim3(grid), dim3(HTHREADS), (size_t)(0), stream, (const IT*)X, (const IT*)W, (OT*)Y, offsets, G, N, K)
     if (in_dtype == VLRF_F32 && out_dtype == VLRF_F32) LAUNCH(float, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_F32) LAUNCH(__nv_bfloat16, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

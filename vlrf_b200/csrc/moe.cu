@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ld_z, int E, int top, int shared_gate, const int* __restrict__ tok_slot,
                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ rank, float* __restrict__ gate,
                  int* __restrict__ counts, int T) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= T) return;
@@ -72,6 +74,8 @@ moe_route_kernel(const float* __restrict__ z, int ld_z, int E, int top, int shar
 }
 
 __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ offsets, int E) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         int at = 0;
         for (int e = 0; e < E; ++e) { offsets[e] = at; at += counts[e]; counts[e] = 0; }
@@ -83,6 +87,8 @@ template <typename ET>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const ET* __restrict__ h, int width, const int* __restrict__ ids, const int* __restrict__ rank,
                   const int* __restrict__ offsets, ET* __restrict__ sorted, int* __restrict__ row_of, int top) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const int pair = blockIdx.x;
     const int e = ids[pair];
     if (e < 0) { if (threadIdx.x == 0) row_of[pair] = -1; return; }
@@ -97,6 +103,8 @@ __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ expert_out, int width, const int* __restrict__ row_of, const float* __restrict__ wts,
                    int top, const float* __restrict__ shared_out, const float* __restrict__ gate, const float* residual,
                    float* y) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < width; i += 128) {
         float s = 0.f;
@@ -117,13 +125,13 @@ extern "C" int vlrf_moe_route(const float* z, int ld_z, int E, int top, int shar
     VLRF_REQUIRE(top > 0 && top <= E && top <= 32, "moe_route: a token takes 1…min(32, experts) experts, not %d of %d", top, E);
     VLRF_REQUIRE(ld_z >= E + (shared_gate ? 1 : 0) && (!shared_gate || gate != nullptr), "moe_route: the logits' rows are too short, or no place for the gate");
     if (T == 0) return VLRF_OK;
-    moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, ld_z, E, top, shared_gate, tok_slot, ids, wts, rank, gate, counts, T);
+    launch_chained(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)(0), stream, z, ld_z, E, top, shared_gate, tok_slot, ids, wts, rank, gate, counts, T);
     return vlrf_check_launch("moe_route");
 }
 
 extern "C" int vlrf_moe_plan(int* counts, int* offsets, int E, cudaStream_t stream) {
     VLRF_REQUIRE(E > 0 && counts != nullptr && offsets != nullptr, "moe_plan: bad arguments");
-    moe_plan_kernel<<<1, 32, 0, stream>>>(counts, offsets, E);
+    launch_chained(moe_plan_kernel, dim3(1), dim3(32), (size_t)(0), stream, counts, offsets, E);
     return vlrf_check_launch("moe_plan");
 }
 
@@ -132,9 +140,9 @@ extern "C" int vlrf_moe_gather(const void* h, int dtype, int width, const int* i
     VLRF_REQUIRE(T >= 0 && width > 0 && top > 0, "moe_gather: bad sizes");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        moe_gather_kernel<float><<<T * top, 128, 0, stream>>>((const float*)h, width, ids, rank, offsets, (float*)sorted, row_of, top);
+        launch_chained(moe_gather_kernel<float>, dim3(T * top), dim3(128), (size_t)(0), stream, (const float*)h, width, ids, rank, offsets, (float*)sorted, row_of, top);
     else if (dtype == VLRF_BF16)
-        moe_gather_kernel<__nv_bfloat16><<<T * top, 128, 0, stream>>>((const __nv_bfloat16*)h, width, ids, rank, offsets, (__nv_bfloat16*)sorted, row_of, top);
+        launch_chained(moe_gather_kernel<__nv_bfloat16>, dim3(T * top), dim3(128), (size_t)(0), stream, (const __nv_bfloat16*)h, width, ids, rank, offsets, (__nv_bfloat16*)sorted, row_of, top);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "moe_gather: unknown dtype %d", dtype);
     return vlrf_check_launch("moe_gather");
 }
@@ -144,6 +152,6 @@ extern "C" int vlrf_moe_combine(const float* expert_out, int width, const int* r
                                 cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && width > 0 && top > 0, "moe_combine: bad sizes");
     if (T == 0) return VLRF_OK;
-    moe_combine_kernel<<<T, 128, 0, stream>>>(expert_out, width, row_of, wts, top, shared_out, gate, residual, y);
+    launch_chained(moe_combine_kernel, dim3(T), dim3(128), (size_t)(0), stream, expert_out, width, row_of, wts, top, shared_out, gate, residual, y);
     return vlrf_check_launch("moe_combine");
 }

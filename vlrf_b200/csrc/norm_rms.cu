@@ -22,6 +22,8 @@ template <typename OT, bool ACC>
 __global__ void __launch_bounds__(NORM_THREADS)
 group_rmsnorm_kernel(const float* y, int ld_y, const int* __restrict__ rows, const float* __restrict__ w, OT* out,
                      int ld_out, int d, int groups, float eps, __nv_bfloat16* also) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     __shared__ float inv_sm[NORM_MAX_GROUPS];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -46,6 +48,8 @@ group_rmsnorm_kernel(const float* y, int ld_y, const int* __restrict__ rows, con
 
 template <typename OT>
 __global__ void cast_rows_kernel(const float* __restrict__ x, OT* __restrict__ out, long long n) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
         const float4 v = *reinterpret_cast<const float4*>(x + i);
@@ -59,6 +63,8 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, OT* __restrict__ o
 // the same, eight bfloat16 a thread (rows and columns on 16-byte boundaries)
 __global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __nv_bfloat16* b, int ldb, __nv_bfloat16* out, int ldo,
                                        int rows, int cols8, int act) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * cols8) return;
     const int r = (int)(i / cols8), c = (int)(i - (long long)r * cols8) * 8;
@@ -78,6 +84,8 @@ __global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __
 
 template <typename ET>
 __global__ void gate_mul_kernel(const ET* a, int lda, const ET* b, int ldb, ET* out, int ldo, int rows, int cols, int act) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * cols) return;
     const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
@@ -97,10 +105,10 @@ extern "C" int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, con
     VLRF_REQUIRE(!accumulate || out_dtype == VLRF_F32, "group_rmsnorm: only float32 rows can be added to");
     if (n_rows == 0) return VLRF_OK;
     if (out_dtype == VLRF_F32) {
-        if (accumulate) group_rmsnorm_kernel<float, true><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
-        else group_rmsnorm_kernel<float, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
+        if (accumulate) launch_chained(group_rmsnorm_kernel<float, true>, dim3(n_rows), dim3(NORM_THREADS), (size_t)(0), stream, y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
+        else launch_chained(group_rmsnorm_kernel<float, false>, dim3(n_rows), dim3(NORM_THREADS), (size_t)(0), stream, y, ld_y, rows, w, (float*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
     } else if (out_dtype == VLRF_BF16) {
-        group_rmsnorm_kernel<__nv_bfloat16, false><<<n_rows, NORM_THREADS, 0, stream>>>(y, ld_y, rows, w, (__nv_bfloat16*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
+        launch_chained(group_rmsnorm_kernel<__nv_bfloat16, false>, dim3(n_rows), dim3(NORM_THREADS), (size_t)(0), stream, y, ld_y, rows, w, (__nv_bfloat16*)out, ld_out, d, groups, eps, (__nv_bfloat16*)also_bf16);
     } else {
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "group_rmsnorm: unknown output dtype %d", out_dtype);
     }
@@ -111,8 +119,8 @@ extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long lon
     VLRF_REQUIRE(n >= 0, "cast_rows: negative size");
     if (n == 0) return VLRF_OK;
     const unsigned blocks = (unsigned)((n + 4 * 256 - 1) / (4 * 256));
-    if (out_dtype == VLRF_BF16) cast_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, n);
-    else if (out_dtype == VLRF_F32) cast_rows_kernel<float><<<blocks, 256, 0, stream>>>(x, (float*)out, n);
+    if (out_dtype == VLRF_BF16) launch_chained(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), (size_t)(0), stream, x, (__nv_bfloat16*)out, n);
+    else if (out_dtype == VLRF_F32) launch_chained(cast_rows_kernel<float>, dim3(blocks), dim3(256), (size_t)(0), stream, x, (float*)out, n);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "cast_rows: unknown output dtype %d", out_dtype);
     return vlrf_check_launch("cast_rows");
 }
@@ -128,12 +136,12 @@ extern "C" int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, voi
                          cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
     if (dtype == VLRF_BF16 && aligned) {
         const long long n8 = n / 8;
-        gate_mul_bf16x8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb,
+        launch_chained(gate_mul_bf16x8_kernel, dim3((unsigned)((n8 + 255) / 256)), dim3(256), (size_t)(0), stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb,
                                                                                (__nv_bfloat16*)out, ldo, rows, cols / 8, act);
     } else if (dtype == VLRF_BF16)
-        gate_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, rows, cols, act);
+        launch_chained(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), (size_t)(0), stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, rows, cols, act);
     else if (dtype == VLRF_F32)
-        gate_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, rows, cols, act);
+        launch_chained(gate_mul_kernel<float>, dim3(blocks), dim3(256), (size_t)(0), stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, rows, cols, act);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul: unknown dtype %d", dtype);
     return vlrf_check_launch("gate_mul");
 }
