@@ -56,6 +56,28 @@ def test_rms_norm_in_groups(d, groups):
     assert torch.equal(z, torch.zeros_like(z))
 
 
+def test_gates_with_float32_inputs_and_ranges_of_wider_rows():
+    from vlrf_b200.csrc import ops
+    g = torch.Generator().manual_seed(2)
+    wide = torch.randn(7, 50, generator=g, dtype=torch.float64) * 3
+    b = torch.randn(7, 20, generator=g, dtype=torch.float64)
+    w32 = dev(wide, torch.float32)
+    for gate, f in (("silu", lambda x: x * torch.sigmoid(x)), ("sigmoid", torch.sigmoid)):
+        out = torch.zeros(7, 20, dtype=torch.bfloat16, device="cuda")
+        ops.gate_mul(w32[:, 3:23], w32[:, 23:43], out, gate, 7, 20)                    # float32, float32 → bfloat16
+        close(out, f(wide[:, 3:23]) * wide[:, 23:43], 5e-3, gate)
+        bb = dev(b, torch.bfloat16)
+        ops.gate_mul(w32[:, 3:23], bb, bb, gate, 7, 20)                                # float32, bfloat16 → in place
+        close(bb, f(wide[:, 3:23]) * dev(b, torch.bfloat16).double().cpu(), 5e-3, gate + " in place")
+        o32 = torch.zeros(7, 20, device="cuda")
+        ops.gate_mul(w32[:, 3:23], w32[:, 23:43], o32, gate, 7, 20)
+        close(o32, f(wide[:, 3:23]) * wide[:, 23:43], 1e-6, gate + " float32")
+        h16 = dev(wide, torch.bfloat16)
+        o16 = torch.zeros(7, 16, dtype=torch.bfloat16, device="cuda")
+        ops.gate_mul(h16[:, 8:24], h16[:, 24:40], o16, gate, 7, 16)                    # all bfloat16, eight a thread
+        close(o16, f(h16[:, 8:24].double().cpu()) * h16[:, 24:40].double().cpu(), 5e-3, gate + " bfloat16")
+
+
 def paged(n_blocks, order, row_w, dt):
     """A latent cache of NaN and a block table that maps slot 1's blocks to `order`."""
     cache = torch.full((n_blocks, 64, row_w), float("nan"), dtype=dt, device="cuda")

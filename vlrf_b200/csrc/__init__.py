@@ -91,7 +91,8 @@ _SIGNATURES = {
     "vlrf_group_rmsnorm": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                            _c_float, _c_int, _c_void_p, _c_void_p],
     "vlrf_cast_rows": [_c_void_p, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
-    "vlrf_gate_mul": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_gate_mul": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                      _c_void_p],
     "vlrf_gemm_heads": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_void_p],
     "vlrf_gemm_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,

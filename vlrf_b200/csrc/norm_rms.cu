@@ -82,17 +82,17 @@ __global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __
     *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <typename ET>
-__global__ void gate_mul_kernel(const ET* a, int lda, const ET* b, int ldb, ET* out, int ldo, int rows, int cols, int act) {
+template <typename AT, typename BT, typename OT>
+__global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, int act) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * cols) return;
     const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
-    const float g = ElemIO<ET>::load(a + (size_t)r * lda + c);
-    const float v = ElemIO<ET>::load(b + (size_t)r * ldb + c);
+    const float g = ElemIO<AT>::load(a + (size_t)r * lda + c);
+    const float v = ElemIO<BT>::load(b + (size_t)r * ldb + c);
     const float f = act == VLRF_ACT_SILU ? silu_f(g) : sigmoid_f(g);
-    ElemIO<ET>::store(out + (size_t)r * ldo + c, f * v);
+    ElemIO<OT>::store(out + (size_t)r * ldo + c, f * v);
 }
 }  // namespace
 
@@ -125,23 +125,25 @@ extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long lon
     return vlrf_check_launch("cast_rows");
 }
 
-extern "C" int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int dtype, int rows,
-                             int cols, int act, cudaStream_t stream) {
+extern "C" int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
+                             int out_dtype, int rows, int cols, int act, cudaStream_t stream) {
     VLRF_REQUIRE(rows >= 0 && cols > 0 && lda >= cols && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
     VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID, "gate_mul: the gate is x*sigmoid(x) or sigmoid(x), not %d", act);
     if (rows == 0) return VLRF_OK;
     const long long n = (long long)rows * cols;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
+    const dim3 blocks((unsigned)((n + 255) / 256));
     const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                          cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
-    if (dtype == VLRF_BF16 && aligned) {
-        const long long n8 = n / 8;
-        launch_chained(gate_mul_bf16x8_kernel, dim3((unsigned)((n8 + 255) / 256)), dim3(256), (size_t)(0), stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb,
-                                                                               (__nv_bfloat16*)out, ldo, rows, cols / 8, act);
-    } else if (dtype == VLRF_BF16)
-        launch_chained(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), (size_t)(0), stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, rows, cols, act);
-    else if (dtype == VLRF_F32)
-        launch_chained(gate_mul_kernel<float>, dim3(blocks), dim3(256), (size_t)(0), stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, rows, cols, act);
-    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul: unknown dtype %d", dtype);
+    typedef __nv_bfloat16 bf;
+#define GO(AT, BT, OT) launch_chained(gate_mul_kernel<AT, BT, OT>, blocks, dim3(256), (size_t)0, stream, (const AT*)a, lda, (const BT*)b, ldb, (OT*)out, ldo, rows, cols, act)
+    if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && aligned)
+        launch_chained(gate_mul_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), (size_t)0, stream, (const bf*)a, lda, (const bf*)b, ldb,
+                       (bf*)out, ldo, rows, cols / 8, act);
+    else if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(bf, bf, bf);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_F32) GO(float, float, float);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(float, bf, bf);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_BF16) GO(float, float, bf);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul: dtypes %d, %d -> %d are not taken", a_dtype, b_dtype, out_dtype);
+#undef GO
     return vlrf_check_launch("gate_mul");
 }

@@ -50,6 +50,15 @@ def _dev(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
 
 
+def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
+    """A matrix whose rows may lie inside wider rows (a range of columns of a product's result): elements of a row
+    contiguous, any row stride."""
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a CUDA matrix whose rows are contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
+
+
 def embed(wte, wpe, tokens, positions, out, dev_err, stats: "RowStats | None" = None) -> None:
     """out[t] = wte[tokens[t]] (+ wpe[positions[t]]), float32.  With `stats` and few rows (a decode step) the rows'
     statistics are left there for the next product's LayerNorm."""
@@ -549,7 +558,7 @@ def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate
     """out[r] (+)= y[rows[r] if rows is given else r] normed in `groups` equal consecutive parts (each divided by
     sqrt(mean(part²) + eps)) and multiplied by weight.  y float32; out float32 or bfloat16 (adding: float32 only).
     out may be y itself.  `also`: a bfloat16 tensor [rows, d] that receives the finished rows as well."""
-    _dev(y, "y", torch.float32); _dev(weight, "weight", torch.float32); _dev(out, "out")
+    _rows(y, "y", torch.float32); _dev(weight, "weight", torch.float32); _dev(out, "out")
     d = y.shape[1]
     n = y.shape[0] if n_rows is None else n_rows
     if rows is not None:
@@ -561,7 +570,7 @@ def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate
         _dev(also, "also", torch.bfloat16)
         if also.shape[1] != d or also.shape[0] < n:
             raise KernelError("group_rmsnorm: the second output does not match")
-    call("vlrf_group_rmsnorm", _ptr(y), d, _ptr(rows), _ptr(weight), _ptr(out), dtype_code(out.dtype), d, n, d, int(groups),
+    call("vlrf_group_rmsnorm", _ptr(y), y.stride(0), _ptr(rows), _ptr(weight), _ptr(out), dtype_code(out.dtype), d, n, d, int(groups),
          float(eps), 1 if accumulate else 0, _ptr(also), _stream())
 
 
@@ -575,12 +584,13 @@ def cast_rows(x, out, n_rows: int) -> None:
 
 def gate_mul(a, b, out, gate: str, n_rows: int, cols: int) -> None:
     """out[r, :cols] = gate(a[r, :cols]) · b[r, :cols]; gate "silu" or "sigmoid".  a, b and out may be column ranges
-    of wider rows (views whose last stride is 1), and out may be a or b."""
+    of wider rows, and out may be a or b.  a and b may be float32 where out is bfloat16 (see the kernel library's header)."""
     for name, t in (("a", a), ("b", b), ("out", out)):
-        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != out.dtype or t.shape[0] < n_rows or t.shape[1] < cols:
+        _rows(t, name)
+        if t.shape[0] < n_rows or t.shape[1] < cols:
             raise KernelError(f"gate_mul: {name} does not match")
-    call("vlrf_gate_mul", _ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(out), out.stride(0), dtype_code(out.dtype),
-         n_rows, cols, GATE[gate], _stream())
+    call("vlrf_gate_mul", _ptr(a), a.stride(0), dtype_code(a.dtype), _ptr(b), b.stride(0), dtype_code(b.dtype), _ptr(out),
+         out.stride(0), dtype_code(out.dtype), n_rows, cols, GATE[gate], _stream())
 
 
 # ---- products per head and per group ---------------------------------------------------------------------------------
@@ -630,7 +640,7 @@ def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
 def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_dims: int, cache, block_table, tok_slot,
                   tok_pos, n_tokens: int, dev_err) -> None:
     """Each token's row [RMSnorm(proj[:C]) · weight | rotate(proj[C:C+R])] into the paged cache [block, BT, row]."""
-    _dev(proj, "proj", torch.float32); _dev(norm_weight, "norm_weight", torch.float32); _dev(cache, "cache")
+    _rows(proj, "proj", torch.float32); _dev(norm_weight, "norm_weight", torch.float32); _dev(cache, "cache")
     _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
     _dev(tok_pos, "tok_pos", torch.int32); _dev(dev_err, "dev_err", torch.int32)
     if inv_freq is not None:
@@ -639,7 +649,7 @@ def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_d
             raise KernelError("latent_append: the table of frequencies is too short")
     if proj.shape[1] < C + R or cache.shape[2] < C + R or norm_weight.shape[0] != C or proj.shape[0] < n_tokens:
         raise KernelError("latent_append: sizes do not match")
-    call("vlrf_latent_append", _ptr(proj), proj.shape[1], C, R, _ptr(norm_weight), float(eps), _ptr(inv_freq), int(rot_dims),
+    call("vlrf_latent_append", _ptr(proj), proj.stride(0), C, R, _ptr(norm_weight), float(eps), _ptr(inv_freq), int(rot_dims),
          _ptr(cache), dtype_code(cache.dtype), cache.shape[2], _ptr(block_table), block_table.shape[1], _ptr(tok_slot),
          _ptr(tok_pos), n_tokens, cache.shape[1], _ptr(dev_err), _stream())
 
@@ -647,12 +657,12 @@ def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_d
 def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, tok_pos, qn, qp, C: int, n_tokens: int) -> None:
     """q float32 [T, H·(dim + R)] → qn [T, H·dim] (unrotated parts) and the last R columns of each head's C + R columns
     of qp (rotated parts, rotated by position)."""
-    _dev(q, "q", torch.float32); _dev(qn, "qn"); _dev(qp, "qp", qn.dtype); _dev(tok_pos, "tok_pos", torch.int32)
+    _rows(q, "q", torch.float32); _dev(qn, "qn"); _dev(qp, "qp", qn.dtype); _dev(tok_pos, "tok_pos", torch.int32)
     if inv_freq is not None:
         _dev(inv_freq, "inv_freq", torch.float32)
     if q.shape[1] != n_heads * (dim + R) or qn.shape[1] != n_heads * dim or qp.shape[1] != n_heads * (C + R):
         raise KernelError("latent_q_rows: sizes do not match")
-    call("vlrf_latent_q_rows", _ptr(q), q.shape[1], n_heads, dim, R, _ptr(inv_freq), int(rot_dims), _ptr(tok_pos), _ptr(qn),
+    call("vlrf_latent_q_rows", _ptr(q), q.stride(0), n_heads, dim, R, _ptr(inv_freq), int(rot_dims), _ptr(tok_pos), _ptr(qn),
          qn.shape[1], _ptr(qp), qp.shape[1], C, dtype_code(qn.dtype), n_tokens, _stream())
 
 
@@ -717,7 +727,7 @@ def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, 
 
 def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts, rank, gate, counts, n_tokens: int) -> None:
     """From float32 router logits z [T, ≥ E (+1)]: ids, wts, rank [T, top], gate [T] (see the kernel library's header)."""
-    _dev(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
+    _rows(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
     _dev(rank, "rank", torch.int32); _dev(counts, "counts", torch.int32)
     if gate is not None:
         _dev(gate, "gate", torch.float32)
@@ -725,7 +735,9 @@ def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts
         _dev(tok_slot, "tok_slot", torch.int32)
     if z.shape[0] < n_tokens or ids.numel() < n_tokens * top or counts.numel() < n_experts:
         raise KernelError("moe_route: sizes do not match")
-    call("vlrf_moe_route", _ptr(z), z.shape[1], n_experts, top, 1 if shared_gate else 0, _ptr(tok_slot), _ptr(ids), _ptr(wts),
+    if z.shape[1] < n_experts + (1 if shared_gate else 0):
+        raise KernelError("moe_route: the logits' rows are too short")
+    call("vlrf_moe_route", _ptr(z), z.stride(0), n_experts, top, 1 if shared_gate else 0, _ptr(tok_slot), _ptr(ids), _ptr(wts),
          _ptr(rank), _ptr(gate), _ptr(counts), n_tokens, _stream())
 
 

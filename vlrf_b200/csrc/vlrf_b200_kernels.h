@@ -185,10 +185,10 @@ int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w
                        int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16, cudaStream_t stream);
 // n float32 numbers to out_dtype.
 int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
-// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU or VLRF_ACT_SIGMOID, all three of `dtype` with row strides of
-// their own (out may be a or b).
-int vlrf_gate_mul(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int dtype, int rows, int cols, int act,
-                  cudaStream_t stream);
+// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU or VLRF_ACT_SIGMOID, each with a row stride of its own (out may be
+// a or b).  Dtypes (a, b → out): all bfloat16; all float32; float32, bfloat16 → bfloat16; float32, float32 → bfloat16.
+int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
+                  int rows, int cols, int act, cudaStream_t stream);
 
 // ---- products per head and per group (gemm_heads.cu) ------------------------------------------------------------------
 // Y[m][h·y_hs …] = X[m][h·x_hs …] · W[h]ᵀ for every head h < H; W [H][N][K].

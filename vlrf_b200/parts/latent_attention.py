@@ -64,6 +64,17 @@ class LatentAttention:
         # Uv per head as it is stored: [H, vdim, kv_rank]
         self.w_uk_t = w_uk.view(H, dim, C).transpose(1, 2).contiguous()
         self.w_uv = w_uv.view(H, vdim, C)
+        # Everything that is a product of the layer's input with float32 results wanted is one product: the queries
+        # (or their latent), the cache row before its norm and rotation, the gate's logits.  (Queries that are used as
+        # they come, without a rotated part or a latent, stay a product of their own in the activation dtype.)
+        first = w_dq if w_dq is not None else (w_q if R > 0 else None)
+        parts, self._cols, at = [], {}, 0
+        for name, m in (("q", first), ("kv", w_dkv), ("gate", w_gate)):
+            if m is not None:
+                parts.append(m)
+                self._cols[name] = (at, at + m.shape[0])
+                at += m.shape[0]
+        self.w_in = torch.cat(parts, dim=0).contiguous() if parts else None
 
     def cache_need(self):
         if self.window > 0:
@@ -83,37 +94,50 @@ class LatentAttention:
         D = C + R
         inv_freq = self.rotary.inv_freq if self.rotary is not None else None
         rot_dims = self.rotary.dims if self.rotary is not None else 0
+        if writes_cache and self.w_dkv is None:
+            raise ValueError("latent attention: a layer without W_dkv reads another layer's cache and cannot write one")
+        # few rows (a decode step): the gate's logits ride in the same product, as float32; many rows: they are a
+        # product of their own in the activation dtype, half the bytes
+        proj, gate_apart = None, self.w_gate is not None and T > ops.SKINNY_MAX_ROWS
+        if self.w_in is not None:
+            n_in = self._cols["gate"][0] if gate_apart else self.w_in.shape[0]
+            if n_in > 0:
+                proj = ws.get("latent_in_proj", T, n_in, torch.float32)
+                ops.linear(h, self.w_in[:n_in], None, proj)
+
+        def cols(name):
+            a, b = self._cols[name]
+            return proj[:, a:b]
+
         if writes_cache:
-            if self.w_dkv is None:
-                raise ValueError("latent attention: a layer without W_dkv reads another layer's cache and cannot write one")
-            proj = ws.get("latent_kv_proj", T, D, torch.float32)
-            ops.linear(h, self.w_dkv, None, proj)
-            ops.latent_append(proj, C, R, self.dkv_norm, self.eps, inv_freq, rot_dims, view.rows, view.block_table,
+            ops.latent_append(cols("kv"), C, R, self.dkv_norm, self.eps, inv_freq, rot_dims, view.rows, view.block_table,
                               ctx.tok_slot, ctx.tok_pos, T, ctx.dev_err)
         # queries: per head [dim | R]
-        q_in, w_qproj = h, self.w_q
-        if self.w_dq is not None:
-            cq32 = ws.get("latent_cq32", T, self.w_dq.shape[0], torch.float32)
-            ops.linear(h, self.w_dq, None, cq32)
-            q_in = ws.get("latent_cq", T, self.w_dq.shape[0], act)
-            ops.group_rmsnorm(cq32, self.dq_norm, self.eps, 1, q_in)
-            w_qproj = self.w_uq
         qp = ws.get("latent_qp", T, H * D, act)
         qn = ws.get("latent_qn", T, H * dim, act)
-        if R == 0:
-            ops.linear(q_in, w_qproj, None, qn)
+        if self.w_dq is not None:
+            cq = ws.get("latent_cq", T, self.w_dq.shape[0], act)
+            ops.group_rmsnorm(cols("q"), self.dq_norm, self.eps, 1, cq)
+            if R == 0:
+                ops.linear(cq, self.w_uq, None, qn)
+            else:
+                q32 = ws.get("latent_q32", T, H * (dim + R), torch.float32)
+                ops.linear(cq, self.w_uq, None, q32)
+                ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
+        elif R == 0:
+            ops.linear(h, self.w_q, None, qn)
         else:
-            q32 = ws.get("latent_q32", T, H * (dim + R), torch.float32)
-            ops.linear(q_in, w_qproj, None, q32)
-            ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
+            ops.latent_q_rows(cols("q"), H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
         ops.linear_heads(qn.view(T, H, dim), self.w_uk_t, qp.view(T, H, D)[:, :, :C], T)
         o = ws.get("latent_o", T, H * C, act)
         ops.attention_latent(qp, view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, o, T, H, self.scale,
                              self.window, ctx.dev_err, ctx=ctx)
         merged = ws.get("attn_out", T, H * vdim, act)
         ops.linear_heads(o.view(T, H, C), self.w_uv, merged.view(T, H, vdim), T)
-        if self.w_gate is not None:
+        if gate_apart:
             g = ws.get("latent_gate", T, H * vdim, act)
             ops.linear(h, self.w_gate, None, g)
             ops.gate_mul(g, merged, merged, "sigmoid", T, H * vdim)
+        elif self.w_gate is not None:
+            ops.gate_mul(cols("gate"), merged, merged, "sigmoid", T, H * vdim)
         ops.linear(merged, self.w_out, None, x, residual=x if accumulate else None)

@@ -51,7 +51,16 @@ class RoutedExperts:
                 w_r = torch.cat([w_router, s_sg.to(w_router.dtype)], dim=0)
                 b_r = torch.cat([b_r, torch.zeros(1, dtype=torch.float32, device=b_r.device)])
                 self.shared_gate = True
-        self.w_router, self.b_router = w_r.contiguous(), b_r.contiguous()
+        # One product of the input gives the router's logits (with the shared gate's) and, for few rows (a decode
+        # step), behind them the shared expert's gate and up rows, all float32; with many rows the shared expert's
+        # are a product of their own in the activation dtype, half the bytes.
+        self.n_logits = w_r.shape[0]
+        if self.shared is not None:
+            w_gu = self.shared[0]
+            self.w_in = torch.cat([w_r, w_gu], dim=0).contiguous()
+            self.b_in = torch.cat([b_r, torch.zeros(w_gu.shape[0], dtype=torch.float32, device=b_r.device)]).contiguous()
+        else:
+            self.w_in, self.b_in = w_r.contiguous(), b_r.contiguous()
 
     fuses_norm = False
     leaves_row_stats = False
@@ -60,8 +69,11 @@ class RoutedExperts:
         T, ws, act = ctx.n_tokens, ctx.ws, ctx.act_dtype
         E, top, width, ff = self.n_experts, self.top, self.width, self.ff
         P = T * top
-        z = ws.get("moe_logits", T, self.w_router.shape[0], torch.float32)
-        ops.linear(h, self.w_router, self.b_router, z)
+        shared_apart = self.shared is not None and T > ops.SKINNY_MAX_ROWS
+        n_in = self.n_logits if shared_apart else self.w_in.shape[0]
+        inp = ws.get("moe_in_proj", T, n_in, torch.float32)
+        ops.linear(h, self.w_in[:n_in], self.b_in[:n_in], inp)
+        z = inp
         ids = ws.get("moe_ids", T, top, torch.int32)
         rank = ws.get("moe_rank", T, top, torch.int32)
         row_of = ws.get("moe_row_of", T, top, torch.int32)
@@ -82,10 +94,14 @@ class RoutedExperts:
         shared_out = None
         if self.shared is not None:
             w_gu, w_d, ffs = self.shared
-            su = ws.get("moe_shared_gate_up", T, 2 * ffs, act)
-            ops.linear(h, w_gu, None, su)
             sa = ws.get("moe_shared_inner", T, ffs, act)
-            ops.gate_mul(su[:, :ffs], su[:, ffs:], sa, "silu", T, ffs)
+            if shared_apart:
+                su = ws.get("moe_shared_gate_up", T, 2 * ffs, act)
+                ops.linear(h, w_gu, None, su)
+                ops.gate_mul(su[:, :ffs], su[:, ffs:], sa, "silu", T, ffs)
+            else:
+                at = self.n_logits
+                ops.gate_mul(inp[:, at:at + ffs], inp[:, at + ffs:at + 2 * ffs], sa, "silu", T, ffs)
             shared_out = ws.get("moe_shared_out", T, width, torch.float32)
             ops.linear(sa, w_d, None, shared_out)
         ops.moe_combine(out, row_of, wts, top, shared_out, gate, x, T, residual=x if accumulate else None)
