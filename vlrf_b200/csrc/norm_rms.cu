@@ -16,7 +16,7 @@
 
 namespace {
 constexpr int NORM_THREADS = 128;
-constexpr int NORM_MAX_GROUPS = 256;
+constexpr int NORM_MAX_GROUPS = 1024;
 
 template <typename OT, bool ACC>
 __global__ void __launch_bounds__(NORM_THREADS)
