@@ -63,8 +63,10 @@ SHARP_FACTOR = 2.0
 MODELS = {"kuv_a": KUV_A, "kuv_b": KUV_B, "kuv_odd": KUV_ODD, "kuv_sharp": KUV_SHARP}
 
 
-def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0) -> None:
-    """The package's random draw for the configuration, the matrices that make queries multiplied by `sharp`."""
+def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0, embedding: float = 1.0) -> None:
+    """The package's random draw for the configuration, the matrices that make queries multiplied by `sharp` and the
+    weight of the norm behind the embedding by `embedding` (with a tied head a token's own embedding otherwise
+    dominates its logits, and every model just repeats its last token)."""
     import vlrf_b200.models  # noqa: F401
     from vlrf_b200.registry import parse_config
     from vlrf_b200.weights import write_safetensors
@@ -73,6 +75,8 @@ def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0) -> None:
     for name in tensors:
         if name.endswith("mix.q") or name.endswith("mix.uq"):
             tensors[name] = tensors[name] * sharp
+        if name == "embed.norm":
+            tensors[name] = tensors[name] * embedding
         if name.endswith("router.b"):
             tensors[name] = tensors[name] * 10.0          # fewer close calls between experts (see the plain decided_prefix)
     Path(out_dir).mkdir(parents=True, exist_ok=True)

@@ -28,7 +28,8 @@ def main(argv=None) -> int:
                     help="bfloat16: the kernels and precisions that serving uses; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens that live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens that live requests hold at any time; the cache is sized for it with room for "
+                         "every request's last, partly filled block of 64 tokens")
     args = ap.parse_args(argv)
 
     print("[trace_run] loading (the first call in a fresh checkout compiles the CUDA kernels)",
@@ -41,7 +42,8 @@ def main(argv=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     model = load_model(args.model, args.dtype, "cuda:0")
-    engine = Engine(model, max_tokens=args.max_tokens)
+    # a sequence holds whole blocks: up to 63 places of its last block are empty, for each of at most 256 live requests
+    engine = Engine(model, max_tokens=args.max_tokens + 64 * min(max(args.max_tokens, 1), 256))
     print("[trace_run] ready", file=sys.stderr, flush=True)
 
     slot_of: dict = {}
