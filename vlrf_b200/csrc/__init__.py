@@ -105,6 +105,7 @@ _SIGNATURES = {
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_latent_mma_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "vlrf_attn_latent_mma_group": [_c_int, _c_int],
+    "vlrf_attn_latent_mma_ctas_per_sm": [_c_int, _c_int],
     "vlrf_attn_latent_mma": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                              _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
                              _c_void_p, _c_void_p],

@@ -319,6 +319,12 @@ extern "C" int vlrf_attn_latent_mma_takes(int C, int R, int row_w, int BT, int l
 extern "C" long long vlrf_attn_latent_mma_scratch_floats(int n_tokens, int H, int C, int n_split) {
     return (long long)n_tokens * ((H + 15) / 16) * n_split * 16 * (C + 2);
 }
+// CTAs of a decode step (one token group each) that an SM holds at a time, by their shared memory and warps.
+extern "C" int vlrf_attn_latent_mma_ctas_per_sm(int C, int R) {
+    const size_t each = lm_smem_bytes(1, C + R) + 1024;
+    const int by_smem = (int)((size_t)227 * 1024 / each);
+    return by_smem < 1 ? 1 : (by_smem > 16 ? 16 : by_smem);
+}
 // Tokens a CTA of a prompt step: the most whose queries fit beside the tiles.
 extern "C" int vlrf_attn_latent_mma_group(int C, int R) {
     return lm_smem_bytes(4, C + R) <= 200 * 1024 ? 4 : 1;

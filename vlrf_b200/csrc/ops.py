@@ -686,14 +686,17 @@ def attention_latent_kind(dtype: torch.dtype, C: int, R: int) -> dict:
     return {"prompt": kind, "decode": kind}
 
 
-def latent_decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
-    """Into how many parts a decode step cuts each context over a latent cache: about two CTAs an SM in all, parts of
-    at least 128 rows."""
+def latent_decode_splits(n_rows: int, n_heads: int, max_context: int, C: int, R: int) -> int:
+    """Into how many parts a decode step cuts each context over a latent cache: as many as keep all CTAs on the SMs at
+    one time (a part more, and the step runs a second, nearly empty wave: 64 rows × 5 parts on 296 places took 50 µs,
+    × 4 parts 45 µs), at most 8, parts of at least 64 rows."""
     forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
     if forced:
         return max(1, min(16, int(forced)))
+    from . import library
     ctas = max(1, n_rows * ((n_heads + 15) // 16))
-    return max(1, min(16, -(-2 * sm_count() // ctas), -(-max_context // 128)))
+    places = sm_count() * library().vlrf_attn_latent_mma_ctas_per_sm(C, R)
+    return max(1, min(8, places // ctas, -(-max_context // 64)))
 
 
 def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, scale: float,
@@ -710,7 +713,7 @@ def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, 
     if ctx is not None and _latent_mma_takes(qp.dtype, C, R, cache.shape[2], cache.shape[1], qp.shape[1]):
         n_split, partials = 1, None
         if ctx.max_new == 1:
-            n_split = latent_decode_splits(ctx.n_seqs, n_heads, ctx.max_context)
+            n_split = latent_decode_splits(ctx.n_seqs, n_heads, ctx.max_context, C, R)
             if n_split > 1:
                 partials = ctx.ws.get("latent_attn_partials", ctx.n_seqs * ((n_heads + 15) // 16) * n_split * 16, C + 2, torch.float32)
         call("vlrf_attn_latent_mma", _ptr(qp), qp.shape[1], _ptr(cache), cache.shape[2], C, R, _ptr(block_table),

@@ -226,6 +226,7 @@ int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void* cache, int
 int vlrf_attn_latent_mma_takes(int C, int R, int row_w, int BT, int ld_q);
 long long vlrf_attn_latent_mma_scratch_floats(int n_tokens, int H, int C, int n_split);
 int vlrf_attn_latent_mma_group(int C, int R);
+int vlrf_attn_latent_mma_ctas_per_sm(int C, int R);     // decode CTAs an SM holds at a time
 int vlrf_attn_latent_mma(const void* qp, int ld_q, const void* cache, int row_w, int C, int R, const int* block_table,
                          int max_blocks, const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
                          int n_seqs, int max_new, int H, int BT, float scale, int window, int n_split, float* partials,
