@@ -485,6 +485,13 @@ def design_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
     asked = 2.0 * pairs * H * (dim + R + vdim)                 # what the design's equations ask for, keys and values per head
     out["attention_prompt"] = {"kuvusun": {"us": round(us, 1), "tflops_done": round(done / us / 1e6, 1), "frac_done": round(done / us / 1e6 / bf16_tflops, 3),
                                            "tflops_asked": round(asked / us / 1e6, 1), "frac_asked": round(asked / us / 1e6 / bf16_tflops, 4)}}
+    # the same step when its sequences begin at position 0: keys and values formed, attention over plain rows
+    if ops.attention_rows_takes(bf, dim, R, vdim, H):
+        qn_, qr_ = torch.randn(T, H * dim, device=dev).to(bf), torch.randn(T, H * R, device=dev).to(bf)
+        kn_, kr_, vv_ = torch.randn(T, H * dim, device=dev).to(bf), torch.randn(T, R, device=dev).to(bf), torch.randn(T, H * vdim, device=dev).to(bf)
+        om = torch.zeros(T, H * vdim, dtype=bf, device=dev)
+        us = timed(lambda i: ops.attention_rows(qn_, qr_, kn_, kr_, vv_, pctx.seq_start, om, S, L, H, dim, R, vdim, 0.1), reps=10)
+        out["attention_prompt"]["kuvusun_rows"] = {"us": round(us, 1), "tflops": round(asked / us / 1e6, 1), "frac": round(asked / us / 1e6 / bf16_tflops, 3)}
     k1, v1 = ks[0][:S * L // 64], vs[0][:S * L // 64]
     qkvp = torch.randn(T, 3 * width, device=dev).to(bf)
     op2 = torch.zeros(T, width, dtype=bf, device=dev)

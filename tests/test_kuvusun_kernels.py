@@ -397,3 +397,63 @@ def test_attention_over_latent_rows_finds_a_key_that_stands_out(C, R, H, dt):
                          scale, 0, err)
     assert float(o2[0].abs().max()) == 0.0 and int(err.item()) == 4
     err.zero_()
+
+
+@pytest.mark.parametrize("dim,R,vdim,H", [(32, 32, 32, 3), (16, 16, 24, 2), (64, 32, 64, 2), (128, 64, 128, 2), (64, 0, 48, 2), (96, 32, 8, 1),
+                                          (192, 64, 128, 1)])
+def test_prompt_attention_over_plain_rows(dim, R, vdim, H):
+    """Sequences of 1 to 200 tokens that begin at position 0, keys in two parts (per head, and one shared by the heads);
+    per query and head one key is made to stand out: the first, the query's own, the last of the tile before, far back."""
+    from vlrf_b200.csrc import ops
+    g = torch.Generator().manual_seed(dim + R + vdim)
+    lens = [1, 70, 64, 200, 33, 65]
+    T = sum(lens)
+    starts = [sum(lens[:i]) for i in range(len(lens) + 1)]
+    bf = torch.bfloat16
+    kn = torch.randn(T, H, dim, generator=g).to(bf)
+    kr = torch.randn(T, R, generator=g).to(bf) if R else None
+    v = torch.randn(T, H, vdim, generator=g).to(bf)
+    scale = 0.29
+    qn = torch.zeros(T, H, dim, dtype=bf)
+    qr = torch.zeros(T, H, R, dtype=bf) if R else None
+    for si, n in enumerate(lens):
+        for i in range(n):
+            for h in range(H):
+                star = [0, i, max(0, (i // 32) * 32 - 1), (i * 7 + h) % (i + 1)][(i + h) % 4]
+                key = torch.cat([kn[starts[si] + star, h].float()] + ([kr[starts[si] + star].float()] if R else []))
+                q = key * (25.0 / (scale * float(key @ key))) + 0.05 * torch.randn(dim + R, generator=g)
+                qn[starts[si] + i, h] = q[:dim].to(bf)
+                if R:
+                    qr[starts[si] + i, h] = q[dim:].to(bf)
+    assert ops.attention_rows_takes(bf, dim, R, vdim, H)
+    out = torch.full((T, H * vdim), float("nan"), dtype=bf, device="cuda")
+    ops.attention_rows(qn.view(T, -1).cuda(), qr.view(T, -1).cuda() if R else None, kn.view(T, -1).cuda(), kr.cuda() if R else None,
+                       v.view(T, -1).cuda(), torch.tensor(starts, dtype=torch.int32, device="cuda"), out, len(lens), max(lens), H, dim, R, vdim, scale)
+    got = out.view(T, H, vdim).double().cpu()
+    assert torch.isfinite(got).all()
+    for si, n in enumerate(lens):
+        a, b = starts[si], starts[si] + n
+        sc = torch.einsum("ihd,jhd->hij", qn[a:b].double(), kn[a:b].double())
+        if R:
+            sc = sc + torch.einsum("ihd,jd->hij", qr[a:b].double(), kr[a:b].double())
+        want = plain.causal_softmax_attention(sc * scale, v[a:b].double())
+        close(got[a:b], want, 1.2e-2, f"sequence of {n}")
+
+
+def test_cache_rows_of_a_step_as_plain_matrices():
+    from vlrf_b200.csrc import ops
+    C, R = 40, 8
+    order = [3, 0, 2, 1]
+    for dt in DT:
+        cache, table = paged(4, order, C + R, dt)
+        rows = torch.randn(256, C + R).to(dt)
+        for b in range(4):
+            cache[order[b]] = rows[64 * b:64 * b + 64].cuda()
+        pos = [0, 63, 64, 200, 255, 5]
+        slot = torch.tensor([1, 1, 1, 1, 1, -1], dtype=torch.int32, device="cuda")
+        oc = torch.full((6, C), 9.0, dtype=dt, device="cuda"); orr = torch.full((6, R), 9.0, dtype=dt, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.latent_gather(cache, C, R, table, slot, torch.tensor(pos, dtype=torch.int32, device="cuda"), oc, orr, 6, err)
+        assert int(err.item()) == 0
+        assert torch.equal(oc[:5].cpu(), rows[pos[:5], :C]) and torch.equal(orr[:5].cpu(), rows[pos[:5], C:])
+        assert float(oc[5].float().abs().max()) == 0.0 and float(orr[5].float().abs().max()) == 0.0

@@ -103,6 +103,11 @@ _SIGNATURES = {
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "vlrf_attn_latent": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
+    "vlrf_latent_gather": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_attn_rows_takes": [_c_int] * 9,
+    "vlrf_attn_rows": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "vlrf_attn_latent_mma_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "vlrf_attn_latent_mma_group": [_c_int, _c_int],
     "vlrf_attn_latent_mma_ctas_per_sm": [_c_int, _c_int],

@@ -103,6 +103,26 @@ latent_q_rows_kernel(const float* __restrict__ q, int ld_q, int H, int dim, int 
     }
 }
 
+// the cache rows of the step's own tokens, as two plain matrices: latents [T][C] and rotated key parts [T][R]
+template <typename ET>
+__global__ void __launch_bounds__(128)
+latent_gather_kernel(const ET* __restrict__ cache, int row_w, int C, int R, const int* __restrict__ block_table, int max_blocks,
+                     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int BT, ET* __restrict__ out_c,
+                     ET* __restrict__ out_r, int* __restrict__ dev_err) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    const int blk = (slot >= 0 && pos >= 0 && pos / BT < max_blocks) ? block_table[(size_t)slot * max_blocks + pos / BT] : -1;
+    if (slot >= 0 && blk < 0 && threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+    const ET* src = cache + ((size_t)max(blk, 0) * BT + (max(pos, 0) % BT)) * row_w;
+    for (int i = threadIdx.x; i < C + R; i += 128) {
+        const ET x = blk >= 0 ? src[i] : ET(0.f);                  // padding rows and lost blocks: zeros
+        if (i < C) out_c[(size_t)t * C + i] = x;
+        else out_r[(size_t)t * R + (i - C)] = x;
+    }
+}
+
 template <typename ET>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 attn_latent_kernel(const ET* __restrict__ qp, int ld_q, const ET* __restrict__ cache, int row_w, int C, int R,
@@ -198,7 +218,7 @@ extern "C" int vlrf_latent_append(const float* proj, int ld, int C, int R, const
 extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims,
                                   const int* tok_pos, void* qn, int ld_qn, void* qp, int ld_qp, int C, int dtype, int T,
                                   cudaStream_t stream) {
-    VLRF_REQUIRE(T >= 0 && H > 0 && dim > 0 && R >= 0 && C > 0, "latent_q_rows: bad sizes");
+    VLRF_REQUIRE(T >= 0 && H > 0 && dim > 0 && R >= 0 && C >= 0, "latent_q_rows: bad sizes");
     VLRF_REQUIRE(ld_q >= H * (dim + R) && ld_qn >= H * dim && ld_qp >= H * (C + R), "latent_q_rows: leading sizes are too small");
     VLRF_REQUIRE(rot_dims >= 0 && rot_dims <= R && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq != nullptr), "latent_q_rows: bad rotation");
     if (T == 0) return VLRF_OK;
@@ -208,6 +228,22 @@ extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int 
         launch_chained(latent_q_rows_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (__nv_bfloat16*)qn, ld_qn, (__nv_bfloat16*)qp, ld_qp, C);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_q_rows: unknown dtype %d", dtype);
     return vlrf_check_launch("latent_q_rows");
+}
+
+extern "C" int vlrf_latent_gather(const void* cache, int dtype, int row_w, int C, int R, const int* block_table, int max_blocks,
+                                  const int* tok_slot, const int* tok_pos, void* out_c, void* out_r, int T, int BT, int* dev_err,
+                                  cudaStream_t stream) {
+    VLRF_REQUIRE(T >= 0 && C > 0 && R >= 0 && row_w >= C + R && BT > 0 && max_blocks > 0 && out_c != nullptr && (R == 0 || out_r != nullptr) &&
+                 dev_err != nullptr, "latent_gather: bad arguments");
+    if (T == 0) return VLRF_OK;
+    if (dtype == VLRF_F32)
+        launch_chained(latent_gather_kernel<float>, dim3(T), dim3(128), (size_t)0, stream, (const float*)cache, row_w, C, R, block_table, max_blocks,
+                       tok_slot, tok_pos, BT, (float*)out_c, (float*)out_r, dev_err);
+    else if (dtype == VLRF_BF16)
+        launch_chained(latent_gather_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)0, stream, (const __nv_bfloat16*)cache, row_w, C, R,
+                       block_table, max_blocks, tok_slot, tok_pos, BT, (__nv_bfloat16*)out_c, (__nv_bfloat16*)out_r, dev_err);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_gather: unknown dtype %d", dtype);
+    return vlrf_check_launch("latent_gather");
 }
 
 extern "C" int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void* cache, int row_w, int C, int R,

@@ -670,6 +670,46 @@ def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, to
 LATENT_MAX_RANK = 1024
 
 
+def latent_gather(cache, C: int, R: int, block_table, tok_slot, tok_pos, out_c, out_r, n_tokens: int, dev_err) -> None:
+    """The step's tokens' cache rows as plain matrices: latents out_c [T, C] and rotated key parts out_r [T, R]."""
+    _dev(cache, "cache"); _dev(out_c, "out_c", cache.dtype); _dev(block_table, "block_table", torch.int32)
+    _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32); _dev(dev_err, "dev_err", torch.int32)
+    if R > 0:
+        _dev(out_r, "out_r", cache.dtype)
+    if cache.shape[2] < C + R or out_c.shape[1] != C or out_c.shape[0] < n_tokens or (R > 0 and (out_r.shape[1] != R or out_r.shape[0] < n_tokens)):
+        raise KernelError("latent_gather: sizes do not match")
+    call("vlrf_latent_gather", _ptr(cache), dtype_code(cache.dtype), cache.shape[2], C, R, _ptr(block_table), block_table.shape[1],
+         _ptr(tok_slot), _ptr(tok_pos), _ptr(out_c), _ptr(out_r) if R > 0 else 0, n_tokens, cache.shape[1], _ptr(dev_err), _stream())
+
+
+#: prompt steps whose sequences all begin at position 0 form keys and values and run the kernel over plain rows (off: the
+#: latent-space kernels take every step)
+LATENT_PROMPT_ROWS = True
+
+
+def attention_rows_takes(dtype: torch.dtype, dim: int, R: int, vdim: int, n_heads: int) -> bool:
+    if dtype != torch.bfloat16 or not LATENT_PROMPT_ROWS:
+        return False
+    from . import library
+    return bool(library().vlrf_attn_rows_takes(dim, R, vdim, n_heads * dim, n_heads * R, n_heads * dim, R, n_heads * vdim, n_heads * vdim))
+
+
+def attention_rows(qn, qr, kn, kr, v, seq_start, out, n_seqs: int, max_new: int, n_heads: int, dim: int, R: int, vdim: int,
+                   scale: float) -> None:
+    """Causal attention of sequences that begin at position 0 over keys and values in plain rows (see the kernel library's
+    header): qn, kn [T, H·dim]; qr [T, H·R], kr [T, R] (None with R = 0); v, out [T, H·vdim]; bfloat16."""
+    for name, t in (("qn", qn), ("kn", kn), ("v", v), ("out", out)):
+        _dev(t, name, torch.bfloat16)
+    if R > 0:
+        _dev(qr, "qr", torch.bfloat16); _dev(kr, "kr", torch.bfloat16)
+    _dev(seq_start, "seq_start", torch.int32)
+    if qn.shape[1] != n_heads * dim or kn.shape[1] != n_heads * dim or v.shape[1] != n_heads * vdim or out.shape[1] != n_heads * vdim \
+            or (R > 0 and (qr.shape[1] != n_heads * R or kr.shape[1] != R)) or seq_start.shape[0] < n_seqs + 1:
+        raise KernelError("attention_rows: sizes do not match")
+    call("vlrf_attn_rows", _ptr(qn), qn.shape[1], _ptr(qr) if R > 0 else 0, n_heads * R, _ptr(kn), kn.shape[1], _ptr(kr) if R > 0 else 0, R,
+         _ptr(v), v.shape[1], _ptr(seq_start), _ptr(out), out.shape[1], n_seqs, max_new, n_heads, dim, R, vdim, float(scale), _stream())
+
+
 LATENT_ATTENTION_MMA = True          # off: every step takes the general kernel (for measurements and cross-checks)
 
 

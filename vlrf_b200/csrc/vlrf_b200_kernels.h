@@ -218,6 +218,19 @@ int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const fl
 int vlrf_attn_latent(const void* qp, int dtype, int ld_q, const void* cache, int row_w, int C, int R, const int* block_table,
                      int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int BT,
                      float scale, int window, int* dev_err, cudaStream_t stream);
+// The cache rows of the step's tokens as plain matrices: out_c [T][C] (latents) and out_r [T][R] (rotated key parts; null
+// with R = 0); rows of padding tokens are zeros.
+int vlrf_latent_gather(const void* cache, int dtype, int row_w, int C, int R, const int* block_table, int max_blocks,
+                       const int* tok_slot, const int* tok_pos, void* out_c, void* out_r, int T, int BT, int* dev_err,
+                       cudaStream_t stream);
+// Prompt attention over keys and values in plain rows (attention_rows.cu; bfloat16, `mma.sync`), for steps whose
+// sequences all begin at their first token: sequence i is the rows seq_start[i] … seq_start[i+1]−1, positions from 0.
+// Queries and keys in two parts: per head qn, kn [T][H·dim]; with a shared key part qr [T][H·R], kr [T][≥ R] (R may be
+// 0).  score = (qn·kn + qr·kr)·scale over keys j ≤ i; v, out [T][H·vdim].  dim + R one of 32, 64, 96, 128, 192, 256.
+int vlrf_attn_rows_takes(int dim, int R, int vdim, int ld_qn, int ld_qr, int ld_kn, int ld_kr, int ld_v, int ld_out);
+int vlrf_attn_rows(const void* qn, int ld_qn, const void* qr, int ld_qr, const void* kn, int ld_kn, const void* kr, int ld_kr,
+                   const void* v, int ld_v, const int* seq_start, void* out, int ld_out, int n_seqs, int max_new, int H, int dim,
+                   int R, int vdim, float scale, cudaStream_t stream);
 // The same on the tensor cores (`mma.sync`, bfloat16; attention_latent_mma.cu): a token's heads are the rows of the
 // MMAs, tiles of 32 cache rows lie in shared memory once for all heads.  Sequence i brings the rows seq_start[i] …
 // seq_start[i+1]−1 at positions seq_pos0[i] … of slot seq_slot[i] (−1: padding, zeros); max_new is the longest run.

@@ -175,7 +175,9 @@ class Engine:
             max_context=max(a + b for a, b in zip(p["pos0"], p["lens"])), logit_rows=views[6],
             n_logit_rows=n_want, act_dtype=self.model.act_dtype, dev_err=self.dev_err, ws=self.ws,
             host_seq_slots=[e.slot for e in entries], host_seq_lens=p["lens"], host_seq_pos0=p["pos0"])
-        logits = self._forward(ctx, (T, B, ctx.max_new, n_want))
+        # (a captured step is replayed for steps of the same sizes; whether every sequence begins at its first token
+        # belongs to them, since parts may launch other kernels for such a step)
+        logits = self._forward(ctx, (T, B, ctx.max_new, n_want, not any(p["pos0"])))
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         self.steps_run += 1

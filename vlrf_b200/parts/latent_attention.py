@@ -64,6 +64,7 @@ class LatentAttention:
         # Uv per head as it is stored: [H, vdim, kv_rank]
         self.w_uk_t = w_uk.view(H, dim, C).transpose(1, 2).contiguous()
         self.w_uv = w_uv.view(H, vdim, C)
+        self.w_uk_rows, self.w_uv_rows = w_uk, w_uv          # as stored, [H·dim, kv_rank] and [H·vdim, kv_rank]: they form keys and values
         # Everything that is a product of the layer's input with float32 results wanted is one product: the queries
         # (or their latent), the cache row before its norm and rotation, the gate's logits.  (Queries that are used as
         # they come, without a rotated part or a latent, stay a product of their own in the activation dtype.)
@@ -112,8 +113,15 @@ class LatentAttention:
         if writes_cache:
             ops.latent_append(cols("kv"), C, R, self.dkv_norm, self.eps, inv_freq, rot_dims, view.rows, view.block_table,
                               ctx.tok_slot, ctx.tok_pos, T, ctx.dev_err)
+        # A prompt step whose sequences all begin at position 0 holds every key and value it needs itself: they are
+        # formed (two products of the step's latents) and attended as plain rows, which takes (dim + R) + vdim
+        # multiplications per query, key and head instead of the latent-space form's (C + R) + C.  Every other step
+        # (a prompt's later portions, decode steps, mixed steps) attends the cache rows in latent space.
+        as_rows = (ctx.max_new > 1 and self.window == 0 and len(ctx.host_seq_pos0) == ctx.n_seqs
+                   and not any(ctx.host_seq_pos0) and ops.attention_rows_takes(act, dim, R, vdim, H))
         # queries: per head [dim | R]
-        qp = ws.get("latent_qp", T, H * D, act)
+        qp = ws.get("latent_qr", T, H * R, act) if as_rows and R > 0 else (None if as_rows else ws.get("latent_qp", T, H * D, act))
+        q_c = 0 if as_rows else C                             # columns ahead of the rotated part in a head's row of qp
         qn = ws.get("latent_qn", T, H * dim, act)
         if self.w_dq is not None:
             cq = ws.get("latent_cq", T, self.w_dq.shape[0], act)
@@ -123,17 +131,27 @@ class LatentAttention:
             else:
                 q32 = ws.get("latent_q32", T, H * (dim + R), torch.float32)
                 ops.linear(cq, self.w_uq, None, q32)
-                ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
+                ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T)
         elif R == 0:
             ops.linear(h, self.w_q, None, qn)
         else:
-            ops.latent_q_rows(cols("q"), H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, C, T)
-        ops.linear_heads(qn.view(T, H, dim), self.w_uk_t, qp.view(T, H, D)[:, :, :C], T)
-        o = ws.get("latent_o", T, H * C, act)
-        ops.attention_latent(qp, view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, o, T, H, self.scale,
-                             self.window, ctx.dev_err, ctx=ctx)
+            ops.latent_q_rows(cols("q"), H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T)
         merged = ws.get("attn_out", T, H * vdim, act)
-        ops.linear_heads(o.view(T, H, C), self.w_uv, merged.view(T, H, vdim), T)
+        if as_rows:
+            rows_c = ws.get("latent_step_c", T, C, act)
+            rows_r = ws.get("latent_step_r", T, R, act) if R > 0 else None
+            ops.latent_gather(view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, rows_c, rows_r, T, ctx.dev_err)
+            kn = ws.get("latent_keys", T, H * dim, act)
+            ops.linear(rows_c, self.w_uk_rows, None, kn)
+            vals = ws.get("latent_values", T, H * vdim, act)
+            ops.linear(rows_c, self.w_uv_rows, None, vals)
+            ops.attention_rows(qn, qp, kn, rows_r, vals, ctx.seq_start, merged, ctx.n_seqs, ctx.max_new, H, dim, R, vdim, self.scale)
+        else:
+            ops.linear_heads(qn.view(T, H, dim), self.w_uk_t, qp.view(T, H, D)[:, :, :C], T)
+            o = ws.get("latent_o", T, H * C, act)
+            ops.attention_latent(qp, view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, o, T, H, self.scale,
+                                 self.window, ctx.dev_err, ctx=ctx)
+            ops.linear_heads(o.view(T, H, C), self.w_uv, merged.view(T, H, vdim), T)
         if gate_apart:
             g = ws.get("latent_gate", T, H * vdim, act)
             ops.linear(h, self.w_gate, None, g)
