@@ -42,7 +42,7 @@ template <int KQ>
 __global__ void __launch_bounds__(128)
 attn_rows_kernel(const __nv_bfloat16* __restrict__ qn, int ld_qn, const __nv_bfloat16* __restrict__ qr, int ld_qr,
                  const __nv_bfloat16* __restrict__ kn, int ld_kn, const __nv_bfloat16* __restrict__ kr, int ld_kr,
-                 const __nv_bfloat16* __restrict__ v, int ld_v, const int* __restrict__ seq_start, int tiles_per_seq,
+                 const __nv_bfloat16* __restrict__ v, int ld_v, const int* __restrict__ seq_start, int n_seqs, int tiles_per_seq,
                  __nv_bfloat16* __restrict__ out, int ld_out, int dim, int R, int vdim, float scale) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
@@ -52,7 +52,8 @@ attn_rows_kernel(const __nv_bfloat16* __restrict__ qn, int ld_qn, const __nv_bfl
     __nv_bfloat16* k_sm = reinterpret_cast<__nv_bfloat16*>(ar_raw);                    // [2][AR_KT][LDK]; first the queries [64][LDK]
     __nv_bfloat16* v_sm = k_sm + (size_t)2 * AR_KT * LDK;                              // [2][AR_KT][ldv]
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int seq = blockIdx.x / tiles_per_seq, q0 = (blockIdx.x % tiles_per_seq) * AR_QT, h = blockIdx.y;
+    // (the tiles of late queries have the most keys: they come first in the grid, so that the short ones fill the end)
+    const int seq = blockIdx.x % n_seqs, q0 = (tiles_per_seq - 1 - blockIdx.x / n_seqs) * AR_QT, h = blockIdx.y;
     const int row0 = seq_start[seq], len = seq_start[seq + 1] - row0;
     if (q0 >= len) return;
     const int q_last = min(q0 + AR_QT, len) - 1;                   // last query of the CTA = last key it needs
@@ -239,7 +240,7 @@ extern "C" int vlrf_attn_rows(const void* qn, int ld_qn, const void* qr, int ld_
         }                                                                                                                      \
         launch_chained(attn_rows_kernel<KQ>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)qn, ld_qn, (const __nv_bfloat16*)qr, \
                        ld_qr, (const __nv_bfloat16*)kn, ld_kn, (const __nv_bfloat16*)kr, ld_kr, (const __nv_bfloat16*)v, ld_v,  \
-                       seq_start, tiles_per_seq, (__nv_bfloat16*)out, ld_out, dim, R, vdim, scale);                            \
+                       seq_start, n_seqs, tiles_per_seq, (__nv_bfloat16*)out, ld_out, dim, R, vdim, scale);                            \
     }
     switch ((dim + R) / 16) {
         case 2: AR_GO(2) break;
