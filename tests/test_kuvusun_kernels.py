@@ -178,7 +178,8 @@ def test_products_per_group(dt):
     assert float((out[P:] - 5.0).abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("M,H,N,K", [(300, 5, 72, 64), (70, 3, 512, 32), (1, 16, 40, 128), (129, 2, 130, 200), (64, 20, 24, 24)])
+@pytest.mark.parametrize("M,H,N,K", [(300, 5, 72, 64), (70, 3, 512, 32), (1, 16, 40, 128), (129, 2, 130, 200), (64, 20, 24, 24),
+                                     (4100, 30, 16, 16)])
 def test_products_per_head_on_the_tensor_cores(M, H, N, K):
     """Shapes that the tcgen05 kernel takes (rows and heads on 16-byte boundaries): heads narrower than the 64 columns
     a copy brings (the neighbour's columns arrive and must count for nothing), row tiles with tails, column tails."""

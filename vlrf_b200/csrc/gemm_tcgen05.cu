@@ -60,7 +60,7 @@ struct TcKvScatter {
 // every group takes all `rows` rows (heads, each with columns of its own).  The row tiles of all groups are listed in
 // shared memory once the kernel ahead has finished (it wrote the offsets); a tile never spans two groups, rows beyond
 // its group's end are computed and not stored, and columns of W beyond N (the next group's rows) likewise.
-constexpr int TC_GR_TAB = 512;       // row tiles of all groups together
+constexpr int TC_GR_TAB = 1024;      // row tiles of all groups together
 struct TcGroups {
     const int* offsets; int G, x_gs, y_gs, rows;
 };
