@@ -164,7 +164,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name):
     no argmax rests on rounding).  The embedding is made quiet, so that what is generated depends on the layers."""
     from vlrf_b200.api import Model
     from vlrf_b200.sampling.params import SamplingParams
-    write_model(MODELS[name], 77, tmp_path, embedding=0.05)
+    write_model(MODELS[name], 77, tmp_path, embedding=0.5)
     cfg, w = plain.read_model_dir(tmp_path)
     prompts = [random_ids(cfg["vocab"], n, 900 + n) for n in (3, 20, 1, 66, 9, 33, 5)]
     new = [6, 3, 9, 4, 7, 2, 8]

@@ -67,12 +67,16 @@ def weight_spec(cfg: KuvusunConfig) -> list[TensorSpec]:
 
 def random_weights(cfg: KuvusunConfig, gen: torch.Generator) -> dict:
     """Matrices N(0, 1/in) (so that every product keeps the scale of its input), norm weights 1 + N(0, 0.1), router
-    biases N(0, 0.1): no term of a formula is hidden by a zero or a one."""
+    biases N(0, 0.1): no term of a formula is hidden by a zero or a one.  The norm behind the embedding is drawn ten
+    times smaller: with the embedding as head a token's own embedding otherwise dominates its logits, and a random
+    model does nothing but repeat its last token whatever its layers compute."""
     out = {}
     for spec in weight_spec(cfg):
         t = torch.randn(spec.shape, generator=gen, dtype=torch.float32)
         if spec.kind == "vector":
             t = 0.1 * t if spec.name.endswith("router.b") else 1.0 + 0.1 * t
+            if spec.name == "embed.norm":
+                t = 0.1 * t
         elif spec.name == "embed":
             pass
         else:
