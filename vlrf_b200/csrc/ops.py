@@ -691,23 +691,34 @@ def attention_rows_takes(dtype: torch.dtype, dim: int, R: int, vdim: int, n_head
     if dtype != torch.bfloat16 or not LATENT_PROMPT_ROWS:
         return False
     from . import library
-    return bool(library().vlrf_attn_rows_takes(dim, R, vdim, n_heads * dim, n_heads * R, n_heads * dim, R, n_heads * vdim, n_heads * vdim))
+    # (as the mixer lays them out: keys and values are column ranges of one product's rows)
+    return (n_heads * dim) % 8 == 0 and bool(library().vlrf_attn_rows_takes(
+        dim, R, vdim, n_heads * dim, n_heads * R, n_heads * (dim + vdim), R, n_heads * (dim + vdim), n_heads * vdim))
+
+
+def attention_rows_strides_ok(dim: int, R: int, vdim: int, ld_qn: int, ld_qr: int, ld_kn: int, ld_kr: int, ld_v: int, ld_out: int) -> bool:
+    from . import library
+    return bool(library().vlrf_attn_rows_takes(dim, R, vdim, ld_qn, ld_qr, ld_kn, ld_kr, ld_v, ld_out))
 
 
 def attention_rows(qn, qr, kn, kr, v, seq_start, out, n_seqs: int, max_new: int, n_heads: int, dim: int, R: int, vdim: int,
                    scale: float) -> None:
     """Causal attention of sequences that begin at position 0 over keys and values in plain rows (see the kernel library's
     header): qn, kn [T, H·dim]; qr [T, H·R], kr [T, R] (None with R = 0); v, out [T, H·vdim]; bfloat16."""
-    for name, t in (("qn", qn), ("kn", kn), ("v", v), ("out", out)):
-        _dev(t, name, torch.bfloat16)
+    for name, t in (("qn", qn), ("kn", kn), ("v", v), ("out", out)):          # (column ranges of wider rows are taken)
+        _rows(t, name, torch.bfloat16)
     if R > 0:
-        _dev(qr, "qr", torch.bfloat16); _dev(kr, "kr", torch.bfloat16)
+        _rows(qr, "qr", torch.bfloat16); _rows(kr, "kr", torch.bfloat16)
     _dev(seq_start, "seq_start", torch.int32)
     if qn.shape[1] != n_heads * dim or kn.shape[1] != n_heads * dim or v.shape[1] != n_heads * vdim or out.shape[1] != n_heads * vdim \
             or (R > 0 and (qr.shape[1] != n_heads * R or kr.shape[1] != R)) or seq_start.shape[0] < n_seqs + 1:
         raise KernelError("attention_rows: sizes do not match")
-    call("vlrf_attn_rows", _ptr(qn), qn.shape[1], _ptr(qr) if R > 0 else 0, n_heads * R, _ptr(kn), kn.shape[1], _ptr(kr) if R > 0 else 0, R,
-         _ptr(v), v.shape[1], _ptr(seq_start), _ptr(out), out.shape[1], n_seqs, max_new, n_heads, dim, R, vdim, float(scale), _stream())
+    lib_takes = attention_rows_strides_ok(dim, R, vdim, qn.stride(0), qr.stride(0) if R > 0 else 8, kn.stride(0), kr.stride(0) if R > 0 else 8,
+                                          v.stride(0), out.stride(0))
+    if not lib_takes:
+        raise KernelError("attention_rows: these sizes or row strides are not taken")
+    call("vlrf_attn_rows", _ptr(qn), qn.stride(0), _ptr(qr) if R > 0 else 0, qr.stride(0) if R > 0 else 0, _ptr(kn), kn.stride(0),
+         _ptr(kr) if R > 0 else 0, kr.stride(0) if R > 0 else 0, _ptr(v), v.stride(0), _ptr(seq_start), _ptr(out), out.stride(0), n_seqs, max_new, n_heads, dim, R, vdim, float(scale), _stream())
 
 
 LATENT_ATTENTION_MMA = True          # off: every step takes the general kernel (for measurements and cross-checks)

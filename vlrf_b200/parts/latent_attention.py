@@ -64,7 +64,8 @@ class LatentAttention:
         # Uv per head as it is stored: [H, vdim, kv_rank]
         self.w_uk_t = w_uk.view(H, dim, C).transpose(1, 2).contiguous()
         self.w_uv = w_uv.view(H, vdim, C)
-        self.w_uk_rows, self.w_uv_rows = w_uk, w_uv          # as stored, [H·dim, kv_rank] and [H·vdim, kv_rank]: they form keys and values
+        # as stored, [H·dim, kv_rank] above [H·vdim, kv_rank]: one product forms a step's keys and values
+        self.w_ukv_rows = torch.cat([w_uk, w_uv], dim=0).contiguous()
         # Everything that is a product of the layer's input with float32 results wanted is one product: the queries
         # (or their latent), the cache row before its norm and rotation, the gate's logits.  (Queries that are used as
         # they come, without a rotated part or a latent, stay a product of their own in the activation dtype.)
@@ -141,11 +142,9 @@ class LatentAttention:
             rows_c = ws.get("latent_step_c", T, C, act)
             rows_r = ws.get("latent_step_r", T, R, act) if R > 0 else None
             ops.latent_gather(view.rows, C, R, view.block_table, ctx.tok_slot, ctx.tok_pos, rows_c, rows_r, T, ctx.dev_err)
-            kn = ws.get("latent_keys", T, H * dim, act)
-            ops.linear(rows_c, self.w_uk_rows, None, kn)
-            vals = ws.get("latent_values", T, H * vdim, act)
-            ops.linear(rows_c, self.w_uv_rows, None, vals)
-            ops.attention_rows(qn, qp, kn, rows_r, vals, ctx.seq_start, merged, ctx.n_seqs, ctx.max_new, H, dim, R, vdim, self.scale)
+            kv = ws.get("latent_keys_values", T, H * (dim + vdim), act)
+            ops.linear(rows_c, self.w_ukv_rows, None, kv)
+            ops.attention_rows(qn, qp, kv[:, :H * dim], rows_r, kv[:, H * dim:], ctx.seq_start, merged, ctx.n_seqs, ctx.max_new, H, dim, R, vdim, self.scale)
         else:
             ops.linear_heads(qn.view(T, H, dim), self.w_uk_t, qp.view(T, H, D)[:, :, :C], T)
             o = ws.get("latent_o", T, H * C, act)
