@@ -8,6 +8,9 @@ by its mixer as a *need*:
              values, with whatever else it keeps per token in the same row): all of them, or the last `window`
   StateNeed  a state of fixed size per sequence (for mixers that carry one)
 
+A mixer that keeps several things (keys and values for one branch, a state for another) says so with a tuple of
+needs; its view then holds one view per need (`CacheView.parts`).
+
 Layers with equal needs form a *group* with storage of its own.  A key/value group owns a pool of
 blocks of `block_tokens` tokens, K and V of shape [layer in group, block, kv_head, block_tokens,
 head_dim] (a latent group: rows of shape [layer in group, block, block_tokens, width]), and a table
@@ -39,6 +42,7 @@ class KVNeed:
     head_dim: int
     kind: str = "full"      # "full" | "window"
     window: int = 0         # for kind "window": a query sees the last `window` keys, itself included
+    v_dim: int = 0          # size of a value where it differs from the keys' head_dim (0: the same)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -63,6 +67,7 @@ class CacheView:
     block_table: torch.Tensor | None = None  # device int32 [slot, block index]
     state: torch.Tensor | None = None        # [slot, *shape]
     rows: torch.Tensor | None = None         # a latent group's [block, block_tokens, width]
+    parts: list | None = None                # for a tuple of needs: one view per need, in its order
 
 
 class _KVGroup:
@@ -75,7 +80,7 @@ class _KVGroup:
         else:
             shape = (len(self.entries), n_blocks, need.n_kv_heads, BLOCK_TOKENS, need.head_dim)
             self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.v = torch.zeros(shape[:-1] + (need.v_dim or need.head_dim,), dtype=dtype, device=device)
             self.rows = None
         # the host's copy of the table lies in pinned memory where there is a GPU, so that bringing the device's
         # copy up to date is an asynchronous copy; `before_write` waits for a copy still reading it
@@ -151,7 +156,11 @@ class SequenceCache:
         for entry, need in enumerate(self.needs):
             if need is None:
                 continue
-            by_need.setdefault(need, []).append(entry)
+            if isinstance(need, tuple):          # several things kept by one mixer: each in the group of its kind
+                for j, part in enumerate(need):
+                    by_need.setdefault(part, []).append((entry, j))
+            else:
+                by_need.setdefault(need, []).append(entry)
         for need, entries in by_need.items():
             if isinstance(need, (KVNeed, LatentNeed)):
                 if need.kind not in ("full", "window"):
@@ -170,7 +179,9 @@ class SequenceCache:
                 self._where[entry] = (g, i)
 
     # -- storage ------------------------------------------------------------------------------
-    def view(self, entry: int) -> CacheView:
+    def view(self, entry) -> CacheView:
+        if not isinstance(entry, tuple) and isinstance(self.needs[entry], tuple):
+            return CacheView(self.needs[entry], parts=[self.view((entry, j)) for j in range(len(self.needs[entry]))])
         if entry not in self._where:
             raise CacheError(f"cache entry {entry} keeps nothing")
         g, i = self._where[entry]
@@ -186,7 +197,7 @@ class SequenceCache:
             if isinstance(g, _KVGroup) and g.rows is not None:
                 total += g.rows.numel() * g.rows.element_size()
             elif isinstance(g, _KVGroup):
-                total += 2 * g.k.numel() * g.k.element_size()
+                total += (g.k.numel() + g.v.numel()) * g.k.element_size()
             else:
                 total += g.state.numel() * g.state.element_size()
         return total
@@ -199,7 +210,7 @@ class SequenceCache:
                 if g.rows is not None:
                     per_tok = len(g.entries) * g.need.width * g.rows.element_size()
                 else:
-                    per_tok = 2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * g.k.element_size()
+                    per_tok = len(g.entries) * g.need.n_kv_heads * (g.need.head_dim + (g.need.v_dim or g.need.head_dim)) * g.k.element_size()
                 for s in slots:
                     n = self.lengths[s]
                     if g.need.kind == "window":

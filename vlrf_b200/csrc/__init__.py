@@ -93,6 +93,22 @@ _SIGNATURES = {
     "vlrf_cast_rows": [_c_void_p, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
     "vlrf_gate_mul": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                       _c_void_p],
+    "vlrf_embed_streams": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_streams_read_norm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                               _c_void_p],
+    "vlrf_streams_write": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_softcap": [_c_void_p, ctypes.c_longlong, _c_float, _c_void_p],
+    "vlrf_qkv_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                             _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                             _c_void_p, _c_void_p],
+    "vlrf_attn_window": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_ssd_conv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                      _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_ssd_gate_norm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_float, _c_float, _c_void_p],
     "vlrf_gemm_heads": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_void_p],
     "vlrf_gemm_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,

@@ -10,11 +10,14 @@
 // sublayer would need.
 //
 // cast_rows: float32 rows to the activation dtype (what a sublayer reads of the float32 residual stream).
-// gate_mul: out = act(a) · b element by element (act: x·sigmoid(x) for gated feed-forwards, sigmoid(x) for gates on
-// an attention's merged heads), float32 arithmetic.
+// gate_mul: out = act(a) · b element by element (act: x·sigmoid(x) or max(x, 0) for gated feed-forwards, sigmoid(x) for
+// gates on an attention's merged heads), float32 arithmetic.
 #include "common.cuh"
 
 namespace {
+__device__ __forceinline__ float gate_f(int act, float g) {
+    return act == VLRF_ACT_SILU ? silu_f(g) : act == VLRF_ACT_SIGMOID ? sigmoid_f(g) : fmaxf(g, 0.f);
+}
 constexpr int NORM_THREADS = 128;
 constexpr int NORM_MAX_GROUPS = 1024;
 
@@ -75,7 +78,7 @@ __global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __
     for (int k = 0; k < 4; ++k) {
         const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
         const float v0 = __uint_as_float(vw[k] << 16), v1 = __uint_as_float(vw[k] & 0xffff0000u);
-        const float f0 = act == VLRF_ACT_SILU ? silu_f(g0) : sigmoid_f(g0), f1 = act == VLRF_ACT_SILU ? silu_f(g1) : sigmoid_f(g1);
+        const float f0 = gate_f(act, g0), f1 = gate_f(act, g1);
         const __nv_bfloat162 p = __floats2bfloat162_rn(f0 * v0, f1 * v1);
         o[k] = *reinterpret_cast<const uint32_t*>(&p);
     }
@@ -91,7 +94,7 @@ __global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* 
     const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
     const float g = ElemIO<AT>::load(a + (size_t)r * lda + c);
     const float v = ElemIO<BT>::load(b + (size_t)r * ldb + c);
-    const float f = act == VLRF_ACT_SILU ? silu_f(g) : sigmoid_f(g);
+    const float f = gate_f(act, g);
     ElemIO<OT>::store(out + (size_t)r * ldo + c, f * v);
 }
 }  // namespace
@@ -128,7 +131,7 @@ extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long lon
 extern "C" int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
                              int out_dtype, int rows, int cols, int act, cudaStream_t stream) {
     VLRF_REQUIRE(rows >= 0 && cols > 0 && lda >= cols && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
-    VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID, "gate_mul: the gate is x*sigmoid(x) or sigmoid(x), not %d", act);
+    VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID || act == VLRF_ACT_RELU, "gate_mul: the gate is x*sigmoid(x), sigmoid(x) or max(x, 0), not %d", act);
     if (rows == 0) return VLRF_OK;
     const long long n = (long long)rows * cols;
     const dim3 blocks((unsigned)((n + 255) / 256));

@@ -15,7 +15,7 @@ from . import KernelError, call
 F32, BF16 = 0, 1
 ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3}
 #: gates of `gate_mul` (not taken by the products' epilogues)
-GATE = {"silu": 4, "sigmoid": 5}
+GATE = {"silu": 4, "sigmoid": 5, "relu": 6}
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -583,7 +583,7 @@ def cast_rows(x, out, n_rows: int) -> None:
 
 
 def gate_mul(a, b, out, gate: str, n_rows: int, cols: int) -> None:
-    """out[r, :cols] = gate(a[r, :cols]) · b[r, :cols]; gate "silu" or "sigmoid".  a, b and out may be column ranges
+    """out[r, :cols] = gate(a[r, :cols]) · b[r, :cols]; gate "silu", "sigmoid" or "relu".  a, b and out may be column ranges
     of wider rows, and out may be a or b.  a and b may be float32 where out is bfloat16 (see the kernel library's header)."""
     for name, t in (("a", a), ("b", b), ("out", out)):
         _rows(t, name)
@@ -819,3 +819,146 @@ def moe_combine(expert_out, row_of, wts, top: int, shared_out, gate, y, n_tokens
         raise KernelError("moe_combine: sizes do not match")
     call("vlrf_moe_combine", _ptr(expert_out), expert_out.shape[1], _ptr(row_of), _ptr(wts), top, _ptr(shared_out), _ptr(gate),
          _ptr(residual), _ptr(y), n_tokens, _stream())
+
+
+# ---- a residual in several streams -------------------------------------------------------------------------------------
+
+def embed_streams(table, tokens, out, streams: int, scale: float, dev_err) -> None:
+    """out[t, s·d …] = table[tokens[t]] · scale for every stream s: float32 [T, streams·d]."""
+    _dev(table, "table"); _dev(tokens, "tokens", torch.int32); _dev(out, "out", torch.float32)
+    _dev(dev_err, "dev_err", torch.int32)
+    T = tokens.shape[0]
+    V, d = table.shape
+    if out.shape[0] < T or out.shape[1] != streams * d:
+        raise KernelError("embed_streams: output does not match")
+    call("vlrf_embed_streams", _ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), T, d, V, int(streams), float(scale),
+         _ptr(dev_err), _stream())
+
+
+def streams_read_norm(x, streams: int, coefficients, weight, eps: float, out, rows=None, n_rows: int | None = None) -> None:
+    """out[r] = RMSnorm(Σ_s coefficients[s] · x[row, s]) · weight, row = rows[r] if rows is given else r; coefficients
+    None: the plain sum.  x float32 [·, streams·d]; out float32 or bfloat16 [n, d]."""
+    _dev(x, "x", torch.float32); _dev(weight, "weight", torch.float32); _dev(out, "out")
+    d = weight.shape[0]
+    n = x.shape[0] if n_rows is None else n_rows
+    if rows is not None:
+        _dev(rows, "rows", torch.int32)
+        n = rows.shape[0]
+    if coefficients is not None:
+        _dev(coefficients, "coefficients", torch.float32)
+        if coefficients.numel() != streams:
+            raise KernelError("streams_read_norm: one coefficient per stream")
+    if x.shape[1] != streams * d or out.shape[1] != d or out.shape[0] < n:
+        raise KernelError("streams_read_norm: sizes do not match")
+    call("vlrf_streams_read_norm", _ptr(x), _ptr(rows), _ptr(coefficients), _ptr(weight), _ptr(out), dtype_code(out.dtype), n, d,
+         int(streams), float(eps), _stream())
+
+
+def streams_write(x, streams: int, mix, out_coefficients, y, n_rows: int) -> None:
+    """x[t, j] ← Σ_s mix[s, j] · x[t, s] + out_coefficients[j] · y[t], every stream j at once from the old ones."""
+    _dev(x, "x", torch.float32); _dev(y, "y", torch.float32); _dev(mix, "mix", torch.float32)
+    _dev(out_coefficients, "out_coefficients", torch.float32)
+    d = y.shape[1]
+    if x.shape[1] != streams * d or tuple(mix.shape) != (streams, streams) or out_coefficients.numel() != streams \
+            or min(x.shape[0], y.shape[0]) < n_rows:
+        raise KernelError("streams_write: sizes do not match")
+    call("vlrf_streams_write", _ptr(x), _ptr(mix), _ptr(out_coefficients), _ptr(y), n_rows, d, int(streams), _stream())
+
+
+def softcap(values, n_rows: int, cap: float) -> None:
+    """values[:n_rows] ← cap · tanh(values / cap), float32, in place."""
+    _dev(values, "values", torch.float32)
+    call("vlrf_softcap", _ptr(values), n_rows * values.shape[1], float(cap), _stream())
+
+
+# ---- attention with key and value sizes of their own ---------------------------------------------------------------------
+
+def qkv_rope_append(proj, q_off: int, k_off: int, v_off: int, freq, rot: int, q_out, k_cache, v_cache, block_table, tok_slot,
+                    tok_pos, n_tokens: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, write_cache: bool, dev_err) -> None:
+    """Queries (rotated) into q_out, keys (rotated) and values into the paged cache, from the float32 rows of a layer's
+    input product.  proj may be a range of columns of wider rows."""
+    _rows(proj, "proj", torch.float32); _dev(q_out, "q_out"); _dev(k_cache, "k_cache", q_out.dtype); _dev(v_cache, "v_cache", q_out.dtype)
+    _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32)
+    nb, hkv, bt, kd = k_cache.shape
+    if hkv != n_kv_heads or kd != dk or tuple(v_cache.shape) != (nb, hkv, bt, dv):
+        raise KernelError("qkv_rope_append: cache shape does not match the heads")
+    if rot > 0:
+        _dev(freq, "freq", torch.float32)
+        if freq.numel() != rot // 2:
+            raise KernelError("qkv_rope_append: one frequency per rotated pair")
+    if proj.shape[0] < n_tokens or q_out.shape[0] < n_tokens:
+        raise KernelError("qkv_rope_append: fewer rows than tokens")
+    call("vlrf_qkv_rope_append", _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(freq) if rot > 0 else 0, int(rot), _ptr(q_out),
+         q_out.shape[1], _ptr(k_cache), _ptr(v_cache), dtype_code(q_out.dtype), _ptr(block_table), block_table.shape[1],
+         _ptr(tok_slot), _ptr(tok_pos), n_tokens, n_heads, n_kv_heads, dk, dv, bt, 1 if write_cache else 0, _ptr(dev_err), _stream())
+
+
+def attention_window(q, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, n_kv_heads: int,
+                     dk: int, dv: int, scale: float, window: int, out_scale: float, dev_err) -> None:
+    """Each token's queries attend the visible keys of its slot; out may be a range of columns of wider rows."""
+    _dev(q, "q"); _dev(k_cache, "k_cache", q.dtype); _dev(v_cache, "v_cache", q.dtype); _rows(out, "out", q.dtype)
+    _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32)
+    nb, hkv, bt, kd = k_cache.shape
+    if hkv != n_kv_heads or kd != dk or tuple(v_cache.shape) != (nb, hkv, bt, dv):
+        raise KernelError("attention_window: cache shape does not match the heads")
+    if out.shape[1] < n_heads * dv or out.shape[0] < n_tokens or q.shape[0] < n_tokens:
+        raise KernelError("attention_window: output does not match")
+    call("vlrf_attn_window", _ptr(q), dtype_code(q.dtype), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+         block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.stride(0), n_tokens, n_heads, n_kv_heads, dk, dv, bt,
+         float(scale), int(window), float(out_scale), _ptr(dev_err), _stream())
+
+
+# ---- a state-space recurrence with a matrix state per head -----------------------------------------------------------------
+
+def ssd_conv(proj, x_off: int, weight, bias, state, conv_off: int, seq_slot, seq_start, seq_pos0, out, n_seqs: int, max_new: int) -> None:
+    """Causal convolution with bias and x·sigmoid(x) over `channels` columns of proj from x_off; leaves the last taps − 1
+    inputs of every sequence in its state row.  state float32 [slots, 2, state_row]."""
+    _rows(proj, "proj", torch.float32); _dev(weight, "weight", torch.float32); _dev(bias, "bias", torch.float32)
+    _dev(state, "state", torch.float32); _dev(out, "out", torch.float32)
+    channels, taps = weight.shape
+    if out.shape[1] != channels or bias.shape[0] != channels or state.dim() != 3 or state.shape[1] != 2:
+        raise KernelError("ssd_conv: sizes do not match")
+    call("vlrf_ssd_conv", _ptr(proj), proj.stride(0), x_off, _ptr(weight), _ptr(bias), _ptr(state), state.shape[2], conv_off,
+         _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), n_seqs, max_new, channels, taps, _stream())
+
+
+def ssd_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, seq_slot, seq_start, seq_pos0, y, n_seqs: int, n_heads: int,
+             n_groups: int, n_state: int, p: int) -> None:
+    """The recurrence over every sequence's new tokens, from and into the state rows; y float32 [T, heads·p]."""
+    _dev(xbc, "xbc", torch.float32); _rows(proj, "proj", torch.float32); _dev(state, "state", torch.float32); _dev(y, "y", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _dev(t, name, torch.float32)
+        if t.numel() != n_heads:
+            raise KernelError(f"ssd_scan: {name} has one number per head")
+    if y.shape[1] != n_heads * p or state.dim() != 3 or state.shape[1] != 2:
+        raise KernelError("ssd_scan: sizes do not match")
+    call("vlrf_ssd_scan", _ptr(xbc), xbc.shape[1], _ptr(proj), proj.stride(0), dt_off, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
+         _ptr(state), state.shape[2], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(y), n_seqs, n_heads, n_groups, n_state, p,
+         _stream())
+
+
+def ssd_gate_norm(y, proj, z_off: int, weight, groups: int, eps: float, factor: float, out, n_rows: int) -> None:
+    """out[r] = factor · groupnorm(y[r] · silu(proj[r, z_off …])) · weight; out may be a range of columns of wider rows."""
+    _dev(y, "y", torch.float32); _rows(proj, "proj", torch.float32); _dev(weight, "weight", torch.float32); _rows(out, "out")
+    d = y.shape[1]
+    if weight.shape[0] != d or out.shape[1] < d or min(y.shape[0], proj.shape[0], out.shape[0]) < n_rows:
+        raise KernelError("ssd_gate_norm: sizes do not match")
+    call("vlrf_ssd_gate_norm", _ptr(y), _ptr(proj), proj.stride(0), z_off, _ptr(weight), _ptr(out), dtype_code(out.dtype), out.stride(0),
+         n_rows, d, int(groups), float(eps), float(factor), _stream())
+
+
+#: largest head size of the attention with key and value sizes of their own; most taps and largest value size of the
+#: state-space kernels
+WINDOW_HEAD_MAX, SSD_MAX_TAPS, SSD_MAX_VDIM = 256, 16, 256
+
+
+def attention_window_kind(dtype: torch.dtype, dk: int, dv: int, n_heads: int, n_kv_heads: int) -> dict:
+    """Which kernels attention with these sizes runs on."""
+    return {"prompt": "CUDA cores", "decode": "CUDA cores"}
+
+
+def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, scale: float,
+                          window: int, out_scale: float) -> None:
+    """The attention of a step (prompt tokens, single tokens or a mix) with the kernel that suits it."""
+    attention_window(q, k_cache, v_cache, block_table, ctx.tok_slot, ctx.tok_pos, out, ctx.n_tokens, n_heads, n_kv_heads, dk, dv,
+                     scale, window, out_scale, ctx.dev_err)

@@ -39,6 +39,7 @@ extern "C" {
 #define VLRF_ACT_LAST_FUSED 3     // the last activation that the products' epilogues take
 #define VLRF_ACT_SILU 4           // x * sigmoid(x): vlrf_gate_mul only
 #define VLRF_ACT_SIGMOID 5        // vlrf_gate_mul only
+#define VLRF_ACT_RELU 6           // max(x, 0): vlrf_gate_mul only
 
 #define VLRF_DEVERR_TOKEN_RANGE 1
 #define VLRF_DEVERR_POSITION_RANGE 2
@@ -185,10 +186,57 @@ int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w
                        int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16, cudaStream_t stream);
 // n float32 numbers to out_dtype.
 int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
-// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU or VLRF_ACT_SIGMOID, each with a row stride of its own (out may be
+// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU, VLRF_ACT_SIGMOID or VLRF_ACT_RELU, each with a row stride of its own (out may be
 // a or b).  Dtypes (a, b → out): all bfloat16; all float32; float32, bfloat16 → bfloat16; float32, float32 → bfloat16.
 int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
                   int rows, int cols, int act, cudaStream_t stream);
+
+// ---- a residual in several streams (streams.cu) -------------------------------------------------------------------------
+// x[t][s] = table[tokens[t]] · scale for every stream s < S: float32 [T][S][d] from a table [V][d] of w_dtype.
+int vlrf_embed_streams(const void* table, int w_dtype, const int* tokens, float* x, int T, int d, int V, int S, float scale,
+                       int* dev_err, cudaStream_t stream);
+// out[r] = u / sqrt(mean(u²) + eps) · w with u = Σ_s a[s] · x[rows ? rows[r] : r][s] (a null: every coefficient 1);
+// x float32 [·][S][d], out of out_dtype [n_rows][d].
+int vlrf_streams_read_norm(const float* x, const int* rows, const float* a, const float* w, void* out, int out_dtype, int n_rows,
+                           int d, int S, float eps, cudaStream_t stream);
+// x[t][j] ← Σ_s mix[s][j] · x[t][s] + b[j] · y[t] for every j at once; x float32 [T][S][d], y float32 [T][d].
+int vlrf_streams_write(float* x, const float* mix, const float* b, const float* y, int T, int d, int S, cudaStream_t stream);
+// v ← cap · tanh(v / cap) over n float32 numbers.
+int vlrf_softcap(float* v, long long n, float cap, cudaStream_t stream);
+
+// ---- attention with key and value sizes of their own (attention_window.cu) -------------------------------------------------
+// From the float32 rows of a layer's input product (queries at q_off: H·dk columns, keys at k_off: Hkv·dk, values at
+// v_off: Hkv·dv): the first `rot` entries of every query and key head rotated by the token's position (entry i with
+// entry i + rot/2, angle position · freq[i]); queries into q_out [T][ldq], keys and values (write_cache ≠ 0) into the
+// paged cache K [block][Hkv][BT][dk], V [block][Hkv][BT][dv]; all of `dtype`.
+int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_off, int v_off, const float* freq, int rot, void* q_out,
+                         int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks, const int* tok_slot,
+                         const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT, int write_cache, int* dev_err,
+                         cudaStream_t stream);
+// out[t][h·dv …] = out_scale · softmax over the visible keys of (q·k · scale) · V: a token sees the keys of its slot at
+// positions ≤ its own (window > 0: the last `window` of them, itself included).  Any dk, dv up to 256.
+int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                     const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
+                     float scale, int window, float out_scale, int* dev_err, cudaStream_t stream);
+
+// ---- a state-space recurrence with a matrix state per head (ssd.cu) ----------------------------------------------------------
+// What a sequence keeps lies in `state`, float32 [slots][2][state_row]: per copy the heads' states [H][N][P] and, at
+// conv_off, the last taps − 1 inputs of the convolution [taps − 1][channels].  A step reads the copy of the parity of
+// the sequence's position at its start (seq_pos0) and writes the copy of the parity at its end.
+// Causal convolution per channel with bias and x·sigmoid(x) over columns x_off … of the float32 rows `proj`; w
+// [channels][taps] (the last tap is the current token's); out float32 [T][channels].  Also leaves the kept inputs.
+int vlrf_ssd_conv(const float* proj, int ld, int x_off, const float* w, const float* bias, float* state, int state_row,
+                  int conv_off, const int* seq_slot, const int* seq_start, const int* seq_pos0, float* out, int n_seqs, int max_new,
+                  int channels, int taps, cudaStream_t stream);
+// The recurrence over every sequence's new tokens.  xbc float32 [T][channels] = [x: H·P | B: G·N | C: G·N]; the step
+// size is softplus(proj[t][dt_off + h] + dt_bias[h]); y float32 [T][H·P].
+int vlrf_ssd_scan(const float* xbc, int channels, const float* proj, int ld, int dt_off, const float* dt_bias, const float* a_log,
+                  const float* D, float* state, int state_row, const int* seq_slot, const int* seq_start, const int* seq_pos0,
+                  float* y, int n_seqs, int Hs, int G, int N, int P, cudaStream_t stream);
+// out[r] = factor · groupnorm(y[r] · silu(proj[r][z_off …])) · w: RMS norm in `groups` equal parts; out of out_dtype
+// with row stride ld_out.
+int vlrf_ssd_gate_norm(const float* y, const float* proj, int ld, int z_off, const float* w, void* out, int out_dtype, int ld_out,
+                       int n_rows, int d, int groups, float eps, float factor, cudaStream_t stream);
 
 // ---- products per head and per group (gemm_heads.cu) ------------------------------------------------------------------
 // Y[m][h·y_hs …] = X[m][h·x_hs …] · W[h]ᵀ for every head h < H; W [H][N][K].

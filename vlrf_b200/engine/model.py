@@ -37,6 +37,9 @@ class DecoderModel:
         self.device = options.device
         self.max_seq_len = int(max_seq_len)
         self.width = embedding.width
+        #: numbers per token of the residual that the embedding writes and the layers rewrite (several streams: a
+        #: multiple of the width; the final norm brings it back to `width`)
+        self.residual_width = int(getattr(embedding, "out_width", embedding.width))
         self.vocab_size = head.vocab_size
         for i, call in enumerate(self.schedule):
             if not (0 <= call.layer < len(self.layers)):
@@ -125,7 +128,7 @@ class DecoderModel:
         """Run the tokens of `ctx` through all scheduled layers; returns float32 logits
         [ctx.n_logit_rows, vocab] for the rows in ctx.logit_rows
         (reference: include/model/transformer.hpp:335-424, which keeps the last row only)."""
-        x = ctx.ws.get("residual", ctx.n_tokens, self.width, torch.float32)
+        x = ctx.ws.get("residual", ctx.n_tokens, self.residual_width, torch.float32)
         ctx.ws.row_stats.forget()                      # nothing is known about the rows of the step before
         ctx.ws.input_cast = None
         self.embedding(ctx, x)

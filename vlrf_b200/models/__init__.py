@@ -1,3 +1,4 @@
 """Architectures.  Importing this package registers them."""
 from . import gpt2  # noqa: F401
 from . import kuvusun  # noqa: F401
+from . import kotisun  # noqa: F401

@@ -1,14 +1,17 @@
-from .block import PreNormBlock, SublayerNormBlock
+from .block import HyperConnectionBlock, PreNormBlock, SublayerNormBlock
 from .context import StepContext, Workspace
 from .embedding import LMHead, TokenEmbedding
-from .feed_forward import DenseMLP
+from .feed_forward import DenseMLP, GatedMLP
 from .latent_attention import LatentAttention
 from .mixer import CausalSelfAttention
 from .moe import RoutedExperts
-from .norm import GroupRMSNorm, LayerNorm
+from .norm import GroupRMSNorm, LayerNorm, StreamSumRMSNorm
+from .parallel import ParallelMixer
 from .position import LearnedAbsolutePositions, RotaryPositions
+from .state_space import StateSpaceMixer
+from .window_attention import WindowAttention
 from .registry import get_part, part_names, register_part, unregister_part
 
-__all__ = ["PreNormBlock", "SublayerNormBlock", "LatentAttention", "RoutedExperts", "GroupRMSNorm", "RotaryPositions", "StepContext", "Workspace", "LMHead", "TokenEmbedding", "DenseMLP",
+__all__ = ["HyperConnectionBlock", "GatedMLP", "StreamSumRMSNorm", "ParallelMixer", "StateSpaceMixer", "WindowAttention", "PreNormBlock", "SublayerNormBlock", "LatentAttention", "RoutedExperts", "GroupRMSNorm", "RotaryPositions", "StepContext", "Workspace", "LMHead", "TokenEmbedding", "DenseMLP",
            "CausalSelfAttention", "LayerNorm", "LearnedAbsolutePositions", "get_part", "part_names",
            "register_part", "unregister_part"]

@@ -43,6 +43,8 @@ class PreNormBlock:
         # that just rewrote them says so; a part with kernels of its own need not know that such a thing exists.
         if not getattr(self.mixer, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
+        if self.feed_forward is None:          # a layer without a feed-forward
+            return
         if getattr(self.feed_forward, "fuses_norm", False):
             self.feed_forward.forward(None, x, ctx, norm=self.norm2)
         else:
@@ -99,3 +101,43 @@ class SublayerNormBlock:
         if self.feed_forward is not None:
             self.feed_forward.forward(self._input(x, ctx), y, ctx, accumulate=False)
             self._add_normed(self.norm2, y, x, ctx)
+
+
+@register_part("block", "hyper_connection")
+class HyperConnectionBlock:
+    """A pre-norm layer over a residual carried in `streams` rows per token, x_1 … x_S [tokens, S·width] float32.
+    Sublayer q (the mixer, then the feed-forward) has read coefficients a_q [S], write coefficients b_q [S] and a mix
+    matrix M_q [S, S] (indexed [from, to]):
+
+        u = Σ_s a_q[s] · x_s,    y = sublayer_q(norm_q(u)),    x_t ← Σ_s M_q[s, t] · x_s + b_q[t] · y   (all t at once).
+
+    The read and the norm are one kernel (`norm1`, `norm2`: "stream_rmsnorm" parts holding a_q); the sublayer leaves
+    y in float32 scratch (`accumulate=False`); the write is one kernel.  The feed-forward may be absent."""
+
+    leaves_row_stats = False
+
+    def __init__(self, norm1, mixer, norm2, feed_forward, *, streams: int, mix1, out1, mix2=None, out2=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.streams = int(streams)
+        self.mix1, self.out1, self.mix2, self.out2 = mix1, out1, mix2, out2
+        if tuple(mix1.shape) != (streams, streams) or out1.numel() != streams:
+            raise ValueError("HyperConnectionBlock: the mix is [streams, streams] and the write coefficients [streams]")
+        if feed_forward is not None and (mix2 is None or out2 is None or norm2 is None):
+            raise ValueError("HyperConnectionBlock: a feed-forward needs its norm and its coefficients")
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+        from ..csrc import ops
+        T, d = ctx.n_tokens, x.shape[1] // self.streams
+        ctx.ws.row_stats.forget()
+        h = ctx.ws.get("block_normed", T, d, ctx.act_dtype)
+        y = ctx.ws.get("block_sublayer_out", T, d, torch.float32)
+        self.norm1(x, h, n_rows=T)
+        self.mixer.forward(h, y, ctx, view, writes_cache, accumulate=False)
+        ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
+        if self.feed_forward is not None:
+            self.norm2(x, h, n_rows=T)
+            self.feed_forward.forward(h, y, ctx, accumulate=False)
+            ops.streams_write(x, self.streams, self.mix2, self.out2, y, T)

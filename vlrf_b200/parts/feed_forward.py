@@ -54,3 +54,34 @@ class DenseMLP:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
             ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
         ops.linear(u, self.w_out, self.b_out, x, residual=x if accumulate else None, stats=ctx.ws.row_stats)
+
+
+GATES = ("silu", "relu", "sigmoid")
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP:
+    """x += (act(h·W_gateᵀ) · (h·W_upᵀ))·W_downᵀ; act "silu", "relu" or "sigmoid".  Gate and up are one product with
+    float32 results, the gate is applied in float32 and the inner rows are rounded once; the residual sum runs in the
+    second product's epilogue (`accumulate=False`: the result replaces x instead)."""
+
+    fuses_norm = False
+    leaves_row_stats = False
+
+    def __init__(self, w_gate, w_up, w_down, *, activation: str):
+        if activation not in GATES:
+            raise ValueError(f"GatedMLP: gate '{activation}' is not one of {', '.join(GATES)}")
+        if w_gate.shape != w_up.shape or w_down.shape[1] != w_gate.shape[0] or w_down.shape[0] != w_gate.shape[1]:
+            raise ValueError("GatedMLP: the three matrices do not chain")
+        self.w_gate_up = torch.cat([w_gate, w_up], dim=0).contiguous()
+        self.w_down = w_down
+        self.activation = activation
+        self.inner = w_gate.shape[0]
+
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, norm=None, accumulate: bool = True) -> None:
+        T, ff = ctx.n_tokens, self.inner
+        gu = ctx.ws.get("ffn_gate_up", T, 2 * ff, torch.float32)
+        ops.linear(h, self.w_gate_up, None, gu)
+        u = ctx.ws.get("ffn_inner", T, ff, ctx.act_dtype)
+        ops.gate_mul(gu[:, :ff], gu[:, ff:], u, self.activation, T, ff)
+        ops.linear(u, self.w_down, None, x, residual=x if accumulate else None)

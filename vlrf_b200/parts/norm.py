@@ -46,3 +46,20 @@ class GroupRMSNorm:
         """also: a bfloat16 tensor that receives the finished rows as well (what the next sublayer reads of them)."""
         ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows, accumulate, also=also)
         return out
+
+
+@register_part("norm", "stream_rmsnorm")
+class StreamSumRMSNorm:
+    """The RMS norm of a weighted sum of a residual's streams: a row of x is `streams` rows of `width` numbers, and
+    y = u / sqrt(mean(u²) + eps) · weight with u = Σ_s coefficients[s] · x_s (coefficients None: the plain sum, which is
+    what a model's last norm reads of such a residual).  One stream without coefficients is the plain RMS norm."""
+
+    def __init__(self, weight: torch.Tensor, eps: float, streams: int = 1, coefficients: torch.Tensor | None = None):
+        if weight.dim() != 1 or streams < 1 or (coefficients is not None and coefficients.numel() != streams):
+            raise ValueError("StreamSumRMSNorm: a weight vector, and one coefficient per stream")
+        self.weight, self.eps, self.streams, self.coefficients = weight, float(eps), int(streams), coefficients
+        self.width = weight.shape[0]
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int | None = None) -> torch.Tensor:
+        ops.streams_read_norm(x, self.streams, self.coefficients, self.weight, self.eps, out, rows, n_rows)
+        return out

@@ -30,15 +30,18 @@ class LearnedAbsolutePositions:
 class RotaryPositions:
     """Rotation of queries and keys by position.  Of a vector's first `dims` entries, entry i is paired with entry
     i + dims/2; at position p the pair (u, v) becomes (u cos a − v sin a, v cos a + u sin a) with a = p · f_i and
-    f_i = base^(−2i/dims); entries beyond `dims` pass unchanged.  The part holds the table f (float32, made in 64-bit);
+    f_i = base^(−2i/dims); entries beyond `dims` pass unchanged.  `scaling_factor` divides every frequency (linear
+    scaling: positions count `scaling_factor` times slower).  The part holds the table f (float32, made in 64-bit);
     the mixer that is given the part applies it inside its own kernels, with angles in float32."""
 
     where = "qk"
 
-    def __init__(self, base: float, dims: int, device):
+    def __init__(self, base: float, dims: int, device, scaling_factor: float = 1.0):
         if dims <= 0 or dims % 2 != 0 or not base > 0.0:
             raise ValueError(f"RotaryPositions: {dims} dimensions cannot be rotated in pairs, or base {base} is not positive")
-        self.base, self.dims = float(base), int(dims)
+        if not scaling_factor > 0.0:
+            raise ValueError(f"RotaryPositions: a scaling factor of {scaling_factor} is not positive")
+        self.base, self.dims, self.scaling_factor = float(base), int(dims), float(scaling_factor)
         half = dims // 2
-        f = torch.tensor([self.base ** (-2.0 * i / dims) for i in range(half)], dtype=torch.float64)
+        f = torch.tensor([self.base ** (-2.0 * i / dims) / self.scaling_factor for i in range(half)], dtype=torch.float64)
         self.inv_freq = f.to(torch.float32).to(device).contiguous()
