@@ -160,7 +160,7 @@ def forward(cfg, w, ids, keep_layers=False):
     T = len(ids)
     eps = cfg["norm"]["eps"]
     positions = torch.arange(T)
-    x0 = w["embed"][torch.tensor(ids)] * cfg["embedding"]["scale"]
+    x0 = w["embed"][torch.tensor(ids)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     S = cfg.get("streams")
     xs = x0[None].repeat(S or 1, 1, 1)
     after = []
@@ -187,3 +187,13 @@ def forward(cfg, w, ids, keep_layers=False):
 
 def logits_all_positions(cfg, w, ids):
     return forward(cfg, w, ids)
+
+
+def greedy_generate(cfg, w, prompt, n_new):
+    """The n_new tokens that taking the largest logit generates (the first maximal index), recomputing everything."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(torch.argmax(forward(cfg, w, ids)[-1]))
+        out.append(t)
+        ids.append(t)
+    return out

@@ -103,6 +103,10 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p],
     "vlrf_attn_window": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_attn_window_mma_takes": [_c_int] * 7,
+    "vlrf_attn_window_mma": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                             _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float,
+                             _c_int, _c_void_p, _c_void_p],
     "vlrf_ssd_conv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "vlrf_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,

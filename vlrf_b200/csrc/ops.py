@@ -952,13 +952,53 @@ def ssd_gate_norm(y, proj, z_off: int, weight, groups: int, eps: float, factor: 
 WINDOW_HEAD_MAX, SSD_MAX_TAPS, SSD_MAX_VDIM = 256, 16, 256
 
 
+#: bfloat16 attention with key and value sizes of their own on the tensor cores where the kernel takes the sizes (off: the
+#: CUDA cores' kernel, which takes everything)
+WINDOW_ATTENTION_MMA = True
+
+
+def _window_mma_takes(dtype, n_heads: int, n_kv_heads: int, dk: int, dv: int, bt: int, ldq: int, ld_out: int) -> bool:
+    if dtype != torch.bfloat16 or not WINDOW_ATTENTION_MMA:
+        return False
+    from . import library
+    return bool(library().vlrf_attn_window_mma_takes(n_heads, n_kv_heads, dk, dv, bt, ldq, ld_out))
+
+
 def attention_window_kind(dtype: torch.dtype, dk: int, dv: int, n_heads: int, n_kv_heads: int) -> dict:
     """Which kernels attention with these sizes runs on."""
-    return {"prompt": "CUDA cores", "decode": "CUDA cores"}
+    kind = "mma.sync" if _window_mma_takes(dtype, n_heads, n_kv_heads, dk, dv, 64, n_heads * dk, n_heads * dv) else "CUDA cores"
+    return {"prompt": kind, "decode": kind}
+
+
+def window_decode_splits(n_rows: int, n_kv_heads: int, max_context: int, window: int) -> int:
+    """Into how many parts a decode step cuts each context for the tensor-core kernel: parts of at least two key tiles,
+    and about two CTAs an SM in all."""
+    forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
+    if forced:
+        return max(1, min(16, int(forced)))
+    reach = min(max_context, window + 63) if window > 0 else max_context
+    tiles = -(-reach // 64)
+    return max(1, min(16, tiles // 2, (2 * sm_count()) // max(1, n_rows * n_kv_heads)))
 
 
 def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, scale: float,
                           window: int, out_scale: float) -> None:
-    """The attention of a step (prompt tokens, single tokens or a mix) with the kernel that suits it."""
+    """The attention of a step (prompt tokens, single tokens or a mix) with the kernel that suits it: bfloat16 sizes that
+    the tensor-core kernel takes go there (a decode step's contexts cut into parts), everything else to the kernel
+    that takes a warp per token and head."""
+    bt = k_cache.shape[2]
+    if _window_mma_takes(q.dtype, n_heads, n_kv_heads, dk, dv, bt, q.shape[1], out.stride(0)) and q.data_ptr() % 16 == 0 \
+            and out.data_ptr() % 4 == 0:
+        _rows(out, "out", q.dtype)
+        n_split, partials = 1, None
+        if ctx.max_new == 1:
+            n_split = window_decode_splits(ctx.n_tokens, n_kv_heads, ctx.max_context, window)
+            if n_split > 1:
+                partials = ctx.ws.get("window_partials", ctx.n_tokens * n_heads * n_split, dv + 2, torch.float32)
+        call("vlrf_attn_window_mma", _ptr(q), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(out), out.stride(0), _ptr(partials), ctx.n_seqs,
+             ctx.max_new, n_heads, n_kv_heads, dk, dv, bt, float(scale), int(window), float(out_scale), n_split, _ptr(ctx.dev_err),
+             _stream())
+        return
     attention_window(q, k_cache, v_cache, block_table, ctx.tok_slot, ctx.tok_pos, out, ctx.n_tokens, n_heads, n_kv_heads, dk, dv,
                      scale, window, out_scale, ctx.dev_err)

@@ -219,6 +219,16 @@ int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const vo
                      const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
                      float scale, int window, float out_scale, int* dev_err, cudaStream_t stream);
 
+// The same attention on the tensor cores (attention_window_mma.cu; bfloat16): a CTA per key/value head, sequence and tile
+// of 64 (token, query head) rows, for prompt steps (rows seq_start[i] … of q are sequence i's new tokens, the first at
+// position seq_pos0[i]; the cache already holds their keys and values) and decode steps (max_new = 1), whose contexts
+// may be cut into n_split parts with float32 scratch `partials` of rows · H · n_split · (dv + 2) numbers.
+int vlrf_attn_window_mma_takes(int H, int Hkv, int dk, int dv, int BT, int ldq, int ld_out);
+int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                         const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
+                         int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale,
+                         int n_split, int* dev_err, cudaStream_t stream);
+
 // ---- a state-space recurrence with a matrix state per head (ssd.cu) ----------------------------------------------------------
 // What a sequence keeps lies in `state`, float32 [slots][2][state_row]: per copy the heads' states [H][N][P] and, at
 // conv_off, the last taps − 1 inputs of the convolution [taps − 1][channels].  A step reads the copy of the parity of

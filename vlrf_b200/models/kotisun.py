@@ -67,7 +67,7 @@ def random_weights(cfg: KotisunConfig, gen: torch.Generator) -> dict:
     S = cfg.streams
     out = {}
     for spec in weight_spec(cfg):
-        if spec.optional and spec.name.split(".")[1].startswith("hc"):
+        if spec.optional:                  # (tensors of a feed-forward that the layer does not have)
             continue
         name, shape = spec.name, spec.shape
         t = torch.randn(shape, generator=gen, dtype=torch.float32)
