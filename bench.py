@@ -325,6 +325,26 @@ def kuvusun_config(z: dict) -> dict:
     return {"architecture": "Kuvusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4}, "layers": layers}
 
 
+#: Kotisun at two sizes that resemble a real model's layers, each beside a GPT-2 of the same width, depth and heads whose
+#: (ungated) feed-forward has about the parameters of the gated one.  Four layers, the middle two run twice.
+KOTISUN_SIZES = {
+    "s": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=96, window=512, rot=32, r_heads=32, r_vdim=64, state=64, groups=4,
+              norm_groups=4, ff_gated=2816, ff=4096, streams=4, vocab=32000),
+    "m": dict(width=2048, heads=16, kv_heads=2, dim=128, vdim=128, window=1024, rot=64, r_heads=32, r_vdim=128, state=128, groups=8,
+              norm_groups=8, ff_gated=5632, ff=8192, streams=4, vocab=32000),
+}
+
+
+def kotisun_config(z: dict) -> dict:
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 2.0}}}
+    right = {"heads": z["r_heads"], "vdim": z["r_vdim"], "state": z["state"], "groups": z["groups"], "conv": 4, "norm_groups": z["norm_groups"]}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7},
+             "mlp": {"kind": "dense", "ff": z["ff_gated"]}}
+    return {"architecture": "Kotisun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "streams": z["streams"], "loop": {"start": 1, "stop": 2, "times": 2}, "logit_softcap": 30.0, "layers": [layer] * 3}
+
+
 def gpt2_config_like(z: dict) -> dict:
     return dict(model_type="gpt2", n_layer=4, n_embd=z["width"], n_head=z["heads"], n_inner=z["ff"], vocab_size=z["vocab"],
                 n_positions=2048, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
@@ -535,23 +555,156 @@ def design_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
     return out
 
 
+def kotisun_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
+    """Kotisun's own kernels alone, each beside the like kernel of GPT-2 at equal width where there is one (timed as in
+    `design_kernels`): windowed attention in a decode step and in a prompt step, the recurrence in both, the
+    convolution, and the reads and writes of the residual's streams beside GPT-2's LayerNorm."""
+    import types
+    import torch
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.parts.context import Workspace
+    dev, bf = "cuda", torch.bfloat16
+    H, G, dk, dv, W, width = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"], z["width"]
+    dev_err = torch.zeros(1, dtype=torch.int32, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+
+    def timed(fn, reps=20):
+        for i in range(3):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3           # microseconds a launch
+
+    def bytes_point(us, nbytes):
+        return {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3), "mib": round(nbytes / 2**20, 1)}
+
+    def flops_point(us, fl):
+        return {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 4)}
+
+    out = {}
+    # -- decode attention: 64 sequences at context 1,024 (of which the window is read) --------------------------------------
+    B, ctxlen = 64, 1024
+    nblk = B * ctxlen // 64
+    table = torch.arange(nblk, dtype=torch.int32, device=dev).view(B, ctxlen // 64).contiguous()
+    slots, pos = i32(list(range(B))), i32([ctxlen - 1] * B)
+    seen = min(W, ctxlen)
+    n_buf = max(2, int(300e6 // (B * seen * G * (dk + dv) * 2)) + 1)
+    ks = [torch.randn(nblk, G, 64, dk, device=dev).to(bf) for _ in range(n_buf)]
+    vs = [torch.randn(nblk, G, 64, dv, device=dev).to(bf) for _ in range(n_buf)]
+    q = torch.randn(B, H * dk, device=dev).to(bf)
+    o = torch.zeros(B, H * dv, dtype=bf, device=dev)
+    ctx = types.SimpleNamespace(n_tokens=B, max_new=1, n_seqs=B, seq_slot=slots, seq_start=i32(list(range(B + 1))), seq_pos0=pos, tok_slot=slots,
+                                tok_pos=pos, max_context=ctxlen, ws=Workspace(dev), dev_err=dev_err)
+    us = timed(lambda i: ops.attention_window_step(q, ks[i % n_buf], vs[i % n_buf], table, o, ctx, H, G, dk, dv, 0.1, W, 1.0))
+    out["attention_decode"] = {"kotisun": bytes_point(us, B * seen * G * (dk + dv) * 2)}
+    del ks, vs
+    dh = width // H
+    n_buf = max(2, int(300e6 // (2 * nblk * H * 64 * dh * 2)) + 1)
+    ks = [torch.randn(nblk, H, 64, dh, device=dev).to(bf) for _ in range(n_buf)]
+    vs = [torch.randn(nblk, H, 64, dh, device=dev).to(bf) for _ in range(n_buf)]
+    qkv = torch.randn(B, 3 * width, device=dev).to(bf)
+    o2 = torch.zeros(B, width, dtype=bf, device=dev)
+    n_split = ops.decode_splits(B, H, ctxlen)
+    ws = Workspace(dev)
+    partials = counters = None
+    if n_split > 1 and ops.attention_decode_needs_scratch(dh, n_split):
+        partials = ws.get("p", B * H * n_split, dh + 2, torch.float32)
+        counters = ws.get_zeroed("c", B * H, torch.int32)
+    us = timed(lambda i: ops.attention_decode(qkv, 0, ks[i % n_buf], vs[i % n_buf], table, slots, pos, o2, B, H, H, dh, 0.1, 0, n_split,
+                                              partials, counters, dev_err))
+    out["attention_decode"]["gpt2"] = bytes_point(us, 2 * B * ctxlen * H * dh * 2)
+    # -- prompt attention: 2 sequences of 1,024 tokens --------------------------------------------------------------------
+    S, L = 2, 1024
+    T = S * L
+    pctx = types.SimpleNamespace(n_tokens=T, max_new=L, n_seqs=S, seq_slot=i32(list(range(S))), seq_start=i32([0, L, 2 * L]), seq_pos0=i32([0, 0]),
+                                 tok_slot=i32([s for s in range(S) for _ in range(L)]), tok_pos=i32(list(range(L)) * S), max_context=L,
+                                 ws=Workspace(dev), dev_err=dev_err)
+    ptable = torch.arange(S * L // 64, dtype=torch.int32, device=dev).view(S, L // 64).contiguous()
+    kp, vp = torch.randn(S * L // 64, G, 64, dk, device=dev).to(bf), torch.randn(S * L // 64, G, 64, dv, device=dev).to(bf)
+    qp = torch.randn(T, H * dk, device=dev).to(bf)
+    op = torch.zeros(T, H * dv, dtype=bf, device=dev)
+    us = timed(lambda i: ops.attention_window_step(qp, kp, vp, ptable, op, pctx, H, G, dk, dv, 0.1, W, 1.0), reps=10)
+    pairs = S * sum(min(i + 1, W) for i in range(L))
+    out["attention_prompt"] = {"kotisun": flops_point(us, 2.0 * pairs * H * (dk + dv))}
+    k1, v1 = ks[0][:S * L // 64], vs[0][:S * L // 64]
+    qkvp = torch.randn(T, 3 * width, device=dev).to(bf)
+    op2 = torch.zeros(T, width, dtype=bf, device=dev)
+    if ops.attention_prefill_takes(bf, dh, 64, 3 * width, 0):
+        n_parts = ops.attention_prefill_parts(bf, S, L, H, dh, 64, 3 * width, 0)
+        pp = cc = None
+        if n_parts > 1:
+            nf, nc = ops.attention_prefill_scratch(S, L, H, n_parts)
+            pp, cc = ws.get("pp", nf, 1, torch.float32), ws.get_zeroed("pc", nc, torch.int32)
+        us = timed(lambda i: ops.attention_prefill(qkvp, 0, k1, v1, ptable, pctx.seq_slot, pctx.seq_start, pctx.seq_pos0, op2, T, S, L, H, H,
+                                                   dh, 0.1, 0, dev_err, n_parts, pp, cc), reps=10)
+        out["attention_prompt"]["gpt2"] = flops_point(us, 4.0 * (S * L * (L + 1) / 2) * H * dh)
+    del ks, vs
+    # -- the recurrence: prompt step (2 × 1,024 tokens) and decode step (64 sequences); bytes: the state read and written, and the rows
+    Hs, P, N, Gs, taps = z["r_heads"], z["r_vdim"], z["state"], z["groups"], 4
+    inner, channels = Hs * P, Hs * P + 2 * Gs * N
+    ld = 2 * inner + 2 * Gs * N + Hs
+    state_row = Hs * N * P + (taps - 1) * channels
+    conv_w, conv_b = torch.randn(channels, taps, device=dev) * 0.3, torch.zeros(channels, device=dev)
+    dt_bias, a_log, dsk = torch.full((Hs,), -1.0, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
+    norm_w = torch.ones(inner, device=dev)
+    for label, c, rows, n_seq, new in (("prompt", pctx, T, S, L), ("decode", ctx, B, B, 1)):
+        n_state = max(2, int(300e6 // (n_seq * 2 * state_row * 4)) + 1) if label == "decode" else 1
+        states = [torch.zeros(n_seq, 2, state_row, device=dev) for _ in range(n_state)]
+        proj = torch.randn(rows, ld, device=dev) * 0.5
+        xbc, y = torch.zeros(rows, channels, device=dev), torch.zeros(rows, inner, device=dev)
+        merged = torch.zeros(rows, inner, dtype=bf, device=dev)
+        us = timed(lambda i: ops.ssd_conv(proj, inner, conv_w, conv_b, states[i % n_state], Hs * N * P, c.seq_slot, c.seq_start, c.seq_pos0, xbc,
+                                          n_seq, new), reps=10)
+        out["conv_" + label] = {"kotisun": bytes_point(us, rows * channels * 8)}
+        us = timed(lambda i: ops.ssd_scan_step(xbc, proj, inner + channels, dt_bias, a_log, dsk, states[i % n_state], c, y, Hs, Gs, N, P), reps=10)
+        nbytes = n_seq * 2 * Hs * N * P * 4 + rows * (channels + inner) * 4
+        fl = 2.0 * rows * Hs * N * P * 2
+        out["scan_" + label] = {"kotisun": dict(bytes_point(us, nbytes), tflops=round(fl / us / 1e6, 2))}
+        us = timed(lambda i: ops.ssd_gate_norm(y, proj, 0, norm_w, z["norm_groups"], 1e-5, 1.0, merged, rows), reps=10)
+        out["gate_norm_" + label] = {"kotisun": bytes_point(us, rows * inner * 10)}
+        del states
+    # -- the residual's streams beside GPT-2's LayerNorm: read + norm, and the write --------------------------------------------
+    St = z["streams"]
+    for label, rows in (("prompt", T), ("decode", B)):
+        n_x = max(2, int(300e6 // (rows * St * width * 4)) + 1)
+        xs = [torch.randn(rows, St * width, device=dev) for _ in range(n_x)]
+        a, w_, mix, b = torch.ones(St, device=dev), torch.ones(width, device=dev), torch.eye(St, device=dev), torch.ones(St, device=dev)
+        h, yv = torch.zeros(rows, width, dtype=bf, device=dev), torch.randn(rows, width, device=dev)
+        us = timed(lambda i: ops.streams_read_norm(xs[i % n_x], St, a, w_, 1e-5, h))
+        out["streams_read_" + label] = {"kotisun": bytes_point(us, rows * width * (4 * St + 2))}
+        us = timed(lambda i: ops.streams_write(xs[i % n_x], St, mix, b, yv, rows))
+        out["streams_write_" + label] = {"kotisun": bytes_point(us, rows * width * (8 * St + 4))}
+        x1 = [torch.randn(rows, width, device=dev) for _ in range(n_x)]
+        us = timed(lambda i: ops.layernorm(x1[i % n_x], w_, w_, 1e-5, h))
+        out["streams_read_" + label]["gpt2"] = bytes_point(us, rows * width * 6)
+        del xs, x1
+    return out
+
+
 def design_bench(args) -> int:
-    """`--design kuvusun`: the design at sizes like a real model's layers (random weights) beside a GPT-2 of equal
+    """`--design NAME`: the design at sizes like a real model's layers (random weights) beside a GPT-2 of equal
     size: prefill and decode throughput, and each kernel's time.  One JSON line."""
     import vlrf_b200.models  # noqa: F401
     from vlrf_b200.weights import write_random_model
     hbm_gbs, bf16_tflops, peak_src = peaks()
     line = {"design": args.design, "beside": "gpt2", "dtype": "bf16", "data": "synthetic (seeded random token ids, random weights)",
             "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": {}}
+    sizes, config_of, kernels_of = {"kuvusun": (DESIGN_SIZES, kuvusun_config, design_kernels),
+                                    "kotisun": (KOTISUN_SIZES, kotisun_config, kotisun_kernels)}[args.design]
     for name in args.design_sizes.split(","):
-        z = DESIGN_SIZES[name]
+        z = sizes[name]
         point = {"sizes": z}
         with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
-            for label, cfg in (() if args.design_only_kernels else (("kuvusun", kuvusun_config(z)), ("gpt2", gpt2_config_like(z)))):
+            for label, cfg in (() if args.design_only_kernels else ((args.design, config_of(z)), ("gpt2", gpt2_config_like(z)))):
                 d = str(write_random_model(cfg, 1234, os.path.join(tmp, label)))
                 point[label] = design_point(d, args.design_prompt, [8, 64], max(8, min(args.steps, 64)), max(3, min(args.warmup, 8)))
         if not args.design_no_kernels:
-            point["kernels"] = design_kernels(z, hbm_gbs, bf16_tflops)
+            point["kernels"] = kernels_of(z, hbm_gbs, bf16_tflops)
         line["sizes"][name] = point
     print(json.dumps(line))
     return 0
@@ -602,7 +755,7 @@ def main() -> int:
                     help="with --only decode or prefill and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
-    ap.add_argument("--design", default=None, choices=["kuvusun"],
+    ap.add_argument("--design", default=None, choices=["kuvusun", "kotisun"],
                     help="instead of the default workload: this design at sizes like a real model's layers beside a GPT-2 of equal size")
     ap.add_argument("--design-sizes", default="s,m", help="with --design: which of the sizes %s" % ",".join(DESIGN_SIZES))
     ap.add_argument("--design-no-kernels", action="store_true", help="with --design: whole steps only, not each kernel alone")

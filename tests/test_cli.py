@@ -95,3 +95,24 @@ def test_run_generates_what_the_plain_implementation_would(model_dirs, plain_mod
             ids.append(tok)
         assert len(ids) == len(prompt) + 6
     assert "12 generated" in out
+
+
+def test_init_and_info_take_a_kotisun_preset(tmp_path, capsys):
+    run_cli(["init", "--config", "kotisun-tiny", "--out", str(tmp_path / "k"), "--seed", "3"], capsys)
+    info = run_cli(["info", "--model", str(tmp_path / "k")], capsys)
+    assert "architecture: Kotisun" in info
+    shown = json.loads(info[info.index("{"):info.rindex("}") + 1])
+    assert shown["streams"] == 3 and shown["loop"] == {"start": 1, "stop": 2, "times": 2} and len(shown["layers"]) == 3
+
+
+@pytest.mark.gpu
+def test_run_generates_with_a_kotisun_model_what_the_plain_implementation_would(tmp_path, capsys):
+    import plain_kotisun
+    run_cli(["init", "--config", "kotisun-tiny", "--out", str(tmp_path / "k"), "--seed", "3"], capsys)
+    cfg, w = plain_kotisun.read_model_dir(tmp_path / "k")
+    f = tmp_path / "prompts.txt"
+    f.write_text("5 17 3 400 44\n7\n")
+    out = run_cli(["run", "--model", str(tmp_path / "k"), "--prompts-file", str(f), "--tokens", "6", "--greedy", "--stop-id", "999",
+                   "--dtype", "float32"], capsys)
+    outputs = [line for prev, line in zip(out.splitlines(), out.splitlines()[1:]) if prev.startswith("--- Output")]
+    assert [[int(t) for t in line.split()] for line in outputs] == [plain_kotisun.greedy_generate(cfg, w, p, 6) for p in ([5, 17, 3, 400, 44], [7])]

@@ -51,6 +51,13 @@ def test_streams_read_write_embed(S, d):
     want = torch.einsum("sj,tsd->tjd", m, xs) + b[None, :, None] * y[:, None, :]
     close(xd.view(T, S, d)[:T - 1], want[:T - 1], 1e-5, "write")
     close(xd.view(T, S, d)[T - 1], xs[T - 1], 1e-7, "rows beyond the step stay")
+    a2, w2 = torch.randn(S, generator=g).double(), torch.randn(d, generator=g).double()
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 6e-3)):
+        xd, h = dev(xs.view(T, S * d)), torch.full((T, d), float("nan"), dtype=dtype, device=DEV)
+        ops.streams_write_read(xd, S, dev(m), dev(b), dev(y), dev(a2), dev(w2), 1e-5, h, T - 1)
+        close(xd.view(T, S, d)[:T - 1], want[:T - 1], 1e-5, "write of write_read")
+        close(h[:T - 1], plain.rms_norm(torch.einsum("j,tjd->td", a2, want), w2, 1e-5)[:T - 1], tol, "read of write_read")
+        close(xd.view(T, S, d)[T - 1], xs[T - 1], 1e-7, "rows beyond the step stay")
     lg = torch.randn(5, 37, generator=g) * 40
     ld = dev(lg)
     ops.softcap(ld, 4, 30.0)

@@ -3,7 +3,7 @@
 // A CTA of four warps takes one key/value head of one sequence and a tile of 64 rows; a row is one (token, query head)
 // pair: the R = H / Hkv query heads that share the key/value head, for 64 / R consecutive new tokens (a decode step has
 // one token, so its rows are the R heads).  Key and value tiles of 64 keys, one cache block each, are read once for all
-// rows by `cp.async` into two stages; S = Q·Kᵀ and O += P·V run on `mma.sync.m16n8k16` with float32 accumulation, the
+// rows by `cp.async` into two stages (up to four in a decode step, whose CTAs have little else to hide the loads behind); S = Q·Kᵀ and O += P·V run on `mma.sync.m16n8k16` with float32 accumulation, the
 // causal and window masks on tiles that touch an edge, the softmax online in float32 (running maximum and sum per row,
 // in units of log2 e), P packed to bfloat16 from the accumulator registers.  Head sizes are padded in shared memory
 // to the next size the kernel is instantiated for (32, 64, 96, 128) with zeros, so any multiple of 8 up to 128 is taken.
@@ -45,7 +45,10 @@ __device__ __forceinline__ uint32_t w_pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int DKP, int DVP>
+// DEC: a tile of at most 16 rows (a decode step: one token, the R heads of the group).  The four warps then share the
+// rows and deal the keys of every tile among themselves, 16 each, and their sums are merged through shared memory.
+// NST: stages of key/value tiles (NST − 1 tiles are under way while one is multiplied).
+template <int DKP, int DVP, bool DEC, int NST>
 __global__ void __launch_bounds__(WM_WARPS * 32)
 attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ Kc,
                        const __nv_bfloat16* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
@@ -53,12 +56,14 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                        __nv_bfloat16* __restrict__ out, int ld_out, float* __restrict__ partials, int H, int Hkv, int dk, int dv,
                        float scale, int window, float out_scale, int n_split, int* __restrict__ dev_err) {
     constexpr int KS = DKP + 8, VS = DVP + 8;       // row strides in elements: 16 bytes of padding keep ldmatrix off bank conflicts
-    constexpr int NT_S = WM_BK / 8, NT_O = DVP / 8, KS_QK = DKP / 16, KS_PV = WM_BK / 16;
+    constexpr int WKEYS = DEC ? WM_BK / WM_WARPS : WM_BK;      // keys of a tile that one warp takes
+    constexpr int NT_S = WKEYS / 8, NT_O = DVP / 8, KS_QK = DKP / 16, KS_PV = WKEYS / 16;
     constexpr int QCH = DKP / 8, VCH = DVP / 8;     // 16-byte pieces of a row
+    constexpr int QROWS = DEC ? 16 : WM_ROWS;       // rows of queries that shared memory holds
     extern __shared__ __align__(16) unsigned char wm_raw[];
-    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(wm_raw);            // [64][KS]
-    __nv_bfloat16* k_tiles = q_tile + WM_ROWS * KS;                              // [2][64][KS]
-    __nv_bfloat16* v_tiles = k_tiles + 2 * WM_BK * KS;                           // [2][64][VS]
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(wm_raw);            // [QROWS][KS]
+    __nv_bfloat16* k_tiles = q_tile + QROWS * KS;                                // [NST][64][KS]
+    __nv_bfloat16* v_tiles = k_tiles + NST * WM_BK * KS;                         // [NST][64][VS]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -78,11 +83,11 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
     const int* table = block_table + (size_t)slot * max_blocks;
     const int n_exist = pos0 + n_new;               // keys of the sequence that the cache holds
 
-    auto load_kv = [&](int i) {                     // all threads: key/value tile number i of this CTA into stage i & 1
+    auto load_kv = [&](int i) {                     // all threads: key/value tile number i of this CTA into stage i % NST
         const int kt = kt_first + part + i * n_split;
         const int blk = table[kt];
-        __nv_bfloat16* kd = k_tiles + (i & 1) * WM_BK * KS;
-        __nv_bfloat16* vd = v_tiles + (i & 1) * WM_BK * VS;
+        __nv_bfloat16* kd = k_tiles + (i % NST) * WM_BK * KS;
+        __nv_bfloat16* vd = v_tiles + (i % NST) * WM_BK * VS;
         if (blk < 0 && threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
         const int valid = n_exist - kt * WM_BK;     // rows of the tile that hold a key of this sequence
         const __nv_bfloat16* ks = Kc + ((size_t)max(blk, 0) * Hkv + hk) * WM_BK * dk;
@@ -99,7 +104,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
         }
     };
     // the rows' queries: row r is token r / R of the tile and query head hk·R + r % R
-    for (int idx = threadIdx.x; idx < WM_ROWS * QCH; idx += WM_WARPS * 32) {
+    for (int idx = threadIdx.x; idx < QROWS * QCH; idx += WM_WARPS * 32) {
         const int r = idx / QCH, ch = idx - r * QCH;
         const int ti = r / R;
         if (ti < n_tok && ch * 8 < dk)
@@ -107,33 +112,37 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
         else
             *reinterpret_cast<uint4*>(q_tile + r * KS + ch * 8) = make_uint4(0, 0, 0, 0);
     }
-    if (n_kt > 0) load_kv(0);
-    cp_commit();
-    if (n_kt > 1) load_kv(1);
-    cp_commit();
+#pragma unroll
+    for (int i = 0; i < NST - 1; ++i) {             // (the queries belong to the first group)
+        if (i < n_kt) load_kv(i);
+        cp_commit();
+    }
 
-    const bool active = warp * 16 < n_tok * R;      // warps whose 16 rows hold no token only help to load
+    const int wrow = DEC ? 0 : warp * 16, wkey = DEC ? warp * WKEYS : 0;          // this warp's first row and first key of a tile
+    const bool active = wrow < n_tok * R;           // warps whose 16 rows hold no token only help to load
     uint32_t qf[KS_QK][4];
     float o[NT_O][4];
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float sl2 = scale * 1.4426950408889634f;  // scores are kept in units of log2(e)
-    const int lr[2] = {warp * 16 + g, warp * 16 + g + 8};                        // this thread's two rows of the tile
+    const int lr[2] = {wrow + g, wrow + g + 8};                                  // this thread's two rows of the tile
     const int q_row[2] = {q_first + lr[0] / R, q_first + lr[1] / R};             // … and their positions
 
     for (int i = 0; i < n_kt; ++i) {
-        cp_wait<1>();                               // everything but the newest group has landed: tile i (and the queries)
-        __syncthreads();
+        cp_wait<NST - 2>();                         // everything but the newest NST − 2 groups has landed: tile i (and the queries)
+        __syncthreads();                            // … for every thread, and every warp is done with tile i − 1
+        if (i + NST - 1 < n_kt) load_kv(i + NST - 1);   // into the stage of tile i − 1
+        cp_commit();                                // (an empty group keeps the count of groups the same for every pass)
         if (i == 0 && active) {
             const uint32_t qb = wsm(q_tile);
 #pragma unroll
             for (int ks = 0; ks < KS_QK; ++ks)
-                w_ldsm_x4(qb + ((warp * 16 + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8) * 2, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+                w_ldsm_x4(qb + ((wrow + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8) * 2, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
         }
         if (active) {
             const int k_base = (kt_first + part + i * n_split) * WM_BK;
-            const uint32_t kb = wsm(k_tiles + (i & 1) * WM_BK * KS), vb = wsm(v_tiles + (i & 1) * WM_BK * VS);
+            const uint32_t kb = wsm(k_tiles + (i % NST) * WM_BK * KS), vb = wsm(v_tiles + (i % NST) * WM_BK * VS);
             float s[NT_S][4];
 #pragma unroll
             for (int j = 0; j < NT_S; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
@@ -143,7 +152,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                 for (int j = 0; j < NT_S; ++j) {
                     // matrices: (keys 8j…, k-step ks: low, high half), (same keys, k-step ks + 1: low, high half)
                     uint32_t b0, b1, b2, b3;
-                    w_ldsm_x4(kb + ((j * 8 + (lane & 7)) * KS + ks * 16 + (lane >> 3) * 8) * 2, b0, b1, b2, b3);
+                    w_ldsm_x4(kb + ((wkey + j * 8 + (lane & 7)) * KS + ks * 16 + (lane >> 3) * 8) * 2, b0, b1, b2, b3);
                     w_mma16816(s[j], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
                     w_mma16816(s[j], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], b2, b3);
                 }
@@ -157,7 +166,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                     const int r = e >> 1;
                     float v = s[j][e] * sl2;
                     if (need_mask) {
-                        const int key = k_base + j * 8 + 2 * t + (e & 1);
+                        const int key = k_base + wkey + j * 8 + 2 * t + (e & 1);
                         if (key > q_row[r] || (window > 0 && key <= q_row[r] - window)) v = -INFINITY;
                     }
                     s[j][e] = v;
@@ -198,17 +207,52 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                 for (int j = 0; j < NT_O; j += 2) {
                     // transposed loads: (keys 16kk…+7, columns 8j…), (keys +8…, same columns), then the same for columns 8(j+1)…
                     uint32_t b0, b1, b2, b3;
-                    w_ldsm_x4_trans(vb + ((kk * 16 + (lane & 15)) * VS + (j + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
+                    w_ldsm_x4_trans(vb + ((wkey + kk * 16 + (lane & 15)) * VS + (j + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
                     w_mma16816(o[j], a0, a1, a2, a3, b0, b1);
                     w_mma16816(o[j + 1], a0, a1, a2, a3, b2, b3);
                 }
             }
         }
-        __syncthreads();                            // every warp is done with this stage
-        if (i + 2 < n_kt) load_kv(i + 2);
-        cp_commit();                                // (an empty group keeps the count of groups the same for every pass)
     }
     cp_wait<0>();
+    if (DEC) {
+        // the warps' sums over their keys meet in shared memory (the tiles are done with): [warp][row][DVP + 2]
+        float* mg = reinterpret_cast<float*>(wm_raw);
+        constexpr int MS = DVP + 2;
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float* dst = mg + ((size_t)warp * 16 + lr[r]) * MS;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) { dst[j * 8 + 2 * t] = o[j][2 * r]; dst[j * 8 + 2 * t + 1] = o[j][2 * r + 1]; }
+            if (t == 0) { dst[DVP] = m_run[r]; dst[DVP + 1] = l_run[r]; }
+        }
+        __syncthreads();
+        const int n_rows = n_tok * R;
+        for (int idx = threadIdx.x; idx < n_rows * (dv + 1); idx += WM_WARPS * 32) {
+            const int row_l = idx / (dv + 1), c = idx - row_l * (dv + 1);       // column dv: the row's maximum and denominator
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WM_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row_l) * MS + DVP]);
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < WM_WARPS; ++w) {
+                const float* src = mg + ((size_t)w * 16 + row_l) * MS;
+                const float f = (src[DVP] == -INFINITY) ? 0.f : exp2f(src[DVP] - M);
+                L = fmaf(src[DVP + 1], f, L);
+                if (c < dv) acc = fmaf(src[c], f, acc);
+            }
+            const int row = row0 + qt * TPT + row_l / R, h = hk * R + row_l % R;
+            if (n_split == 1) {
+                if (c < dv) out[(size_t)row * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * (out_scale / L) : 0.f);
+            } else {
+                float* dst = partials + (((size_t)row * H + h) * n_split + part) * (dv + 2);
+                if (c < dv) dst[c] = acc;
+                else { dst[dv] = M; dst[dv + 1] = L; }
+            }
+        }
+        return;
+    }
     if (!active) return;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -258,13 +302,15 @@ attn_window_merge_kernel(const float* __restrict__ partials, const int* __restri
     }
 }
 
-template <int DKP, int DVP>
+template <int DKP, int DVP, bool DEC>
 int launch_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                       const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                       int n_seqs, int max_new, int H, int Hkv, int dk, int dv, float scale, int window, float out_scale, int n_split,
                       int* dev_err, cudaStream_t stream) {
-    const size_t smem = (size_t)(3 * 64 * (DKP + 8) + 2 * 64 * (DVP + 8)) * 2;
-    auto kern = attn_window_mma_kernel<DKP, DVP>;
+    // stages of a decode step: as many as leave room for two or three CTAs an SM
+    constexpr int NST = DEC ? (DKP + DVP <= 160 ? 4 : DKP + DVP <= 224 ? 3 : 2) : 2;
+    const size_t smem = (size_t)((DEC ? 16 : 64) * (DKP + 8) + NST * 64 * (DKP + 8) + NST * 64 * (DVP + 8)) * 2;
+    auto kern = attn_window_mma_kernel<DKP, DVP, DEC, NST>;
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -302,7 +348,10 @@ extern "C" int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, cons
     if (n_seqs == 0 || max_new == 0) return VLRF_OK;
     const int kp = dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 96 ? 96 : 128, vp = dv <= 32 ? 32 : dv <= 64 ? 64 : dv <= 96 ? 96 : 128;
     int st = VLRF_ERR_UNSUPPORTED;
-#define GO(A, B) if (kp == A && vp == B) st = launch_window_mma<A, B>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
+    const bool dec = max_new == 1 && H / Hkv <= 16;            // every tile holds one token's heads: the warps deal the keys
+#define GO(A, B) if (kp == A && vp == B) st = dec ? launch_window_mma<A, B, true>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
+        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, dev_err, stream) \
+        : launch_window_mma<A, B, false>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
         out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, dev_err, stream);
     GO(32, 32) GO(32, 64) GO(32, 96) GO(32, 128) GO(64, 32) GO(64, 64) GO(64, 96) GO(64, 128)
     GO(96, 32) GO(96, 64) GO(96, 96) GO(96, 128) GO(128, 32) GO(128, 64) GO(128, 96) GO(128, 128)

@@ -865,6 +865,20 @@ def streams_write(x, streams: int, mix, out_coefficients, y, n_rows: int) -> Non
     call("vlrf_streams_write", _ptr(x), _ptr(mix), _ptr(out_coefficients), _ptr(y), n_rows, d, int(streams), _stream())
 
 
+def streams_write_read(x, streams: int, mix, out_coefficients, y, coefficients, weight, eps: float, out, n_rows: int) -> None:
+    """`streams_write` followed by `streams_read_norm` of the same rows with the next sublayer's coefficients and norm
+    weight, in one pass over the streams."""
+    _dev(x, "x", torch.float32); _dev(y, "y", torch.float32); _dev(mix, "mix", torch.float32); _dev(out, "out")
+    _dev(out_coefficients, "out_coefficients", torch.float32); _dev(coefficients, "coefficients", torch.float32)
+    _dev(weight, "weight", torch.float32)
+    d = y.shape[1]
+    if x.shape[1] != streams * d or tuple(mix.shape) != (streams, streams) or out_coefficients.numel() != streams \
+            or coefficients.numel() != streams or weight.shape[0] != d or out.shape[1] != d or min(x.shape[0], y.shape[0], out.shape[0]) < n_rows:
+        raise KernelError("streams_write_read: sizes do not match")
+    call("vlrf_streams_write_read", _ptr(x), _ptr(mix), _ptr(out_coefficients), _ptr(y), _ptr(coefficients), _ptr(weight), _ptr(out),
+         dtype_code(out.dtype), n_rows, d, int(streams), float(eps), _stream())
+
+
 def softcap(values, n_rows: int, cap: float) -> None:
     """values[:n_rows] ← cap · tanh(values / cap), float32, in place."""
     _dev(values, "values", torch.float32)
@@ -923,7 +937,7 @@ def ssd_conv(proj, x_off: int, weight, bias, state, conv_off: int, seq_slot, seq
 
 
 def ssd_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, seq_slot, seq_start, seq_pos0, y, n_seqs: int, n_heads: int,
-             n_groups: int, n_state: int, p: int) -> None:
+             n_groups: int, n_state: int, p: int, max_new: int = 16) -> None:
     """The recurrence over every sequence's new tokens, from and into the state rows; y float32 [T, heads·p]."""
     _dev(xbc, "xbc", torch.float32); _rows(proj, "proj", torch.float32); _dev(state, "state", torch.float32); _dev(y, "y", torch.float32)
     for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
@@ -933,8 +947,8 @@ def ssd_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, seq_slot, se
     if y.shape[1] != n_heads * p or state.dim() != 3 or state.shape[1] != 2:
         raise KernelError("ssd_scan: sizes do not match")
     call("vlrf_ssd_scan", _ptr(xbc), xbc.shape[1], _ptr(proj), proj.stride(0), dt_off, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
-         _ptr(state), state.shape[2], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(y), n_seqs, n_heads, n_groups, n_state, p,
-         _stream())
+         _ptr(state), state.shape[2], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(y), n_seqs, int(max_new), n_heads, n_groups,
+         n_state, p, _stream())
 
 
 def ssd_gate_norm(y, proj, z_off: int, weight, groups: int, eps: float, factor: float, out, n_rows: int) -> None:
@@ -972,12 +986,13 @@ def attention_window_kind(dtype: torch.dtype, dk: int, dv: int, n_heads: int, n_
 
 def window_decode_splits(n_rows: int, n_kv_heads: int, max_context: int, window: int) -> int:
     """Into how many parts a decode step cuts each context for the tensor-core kernel: parts of at least two key tiles,
-    and about two CTAs an SM in all."""
+    about two CTAs an SM in all."""
     forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
     if forced:
         return max(1, min(16, int(forced)))
     reach = min(max_context, window + 63) if window > 0 else max_context
     tiles = -(-reach // 64)
+    # (a part costs a second kernel that merges them: parts only where the step's CTAs would not fill the GPU otherwise)
     return max(1, min(16, tiles // 2, (2 * sm_count()) // max(1, n_rows * n_kv_heads)))
 
 
@@ -1002,3 +1017,9 @@ def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: i
         return
     attention_window(q, k_cache, v_cache, block_table, ctx.tok_slot, ctx.tok_pos, out, ctx.n_tokens, n_heads, n_kv_heads, dk, dv,
                      scale, window, out_scale, ctx.dev_err)
+
+
+def ssd_scan_step(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, ctx, y, n_heads: int, n_groups: int, n_state: int, p: int) -> None:
+    """The recurrence of a step with the kernel that suits it."""
+    ssd_scan(xbc, proj, dt_off, dt_bias, a_log, d_skip, state, ctx.seq_slot, ctx.seq_start, ctx.seq_pos0, y, ctx.n_seqs, n_heads,
+             n_groups, n_state, p, ctx.max_new)

@@ -13,16 +13,18 @@
 // step of one token (or any odd number) leaves what it read untouched and may be run again with the same result.
 //
 //   ssd_conv        causal convolution per channel over the float32 projection's columns (zeros, or the kept inputs,
-//                   before the step's first token), bias, x·sigmoid(x); one thread per channel and run of 64 tokens
+//                   before the step's first token), bias, x·sigmoid(x); one thread per channel and run of 16 tokens
 //   ssd_conv_state  the last taps − 1 inputs of every sequence into the copy the step writes
-//   ssd_scan        the recurrence, token by token: a CTA per (head, sequence), the state in registers (thread (p, j)
-//                   holds the rows j, j + NS, … of column p), C-weighted column sums over the NS threads of a column
-//                   through shared memory; serves prompts and single tokens alike
+//   ssd_scan        the recurrence, token by token: a CTA per (head, 32 columns of the state, sequence), a lane per
+//                   column, a warp per slice of rows, the state in registers; the inputs of 16 tokens at a time arrive in
+//                   shared memory by `cp.async` a batch ahead, B and C are read from there by every lane alike; the
+//                   C-weighted sums of the slices meet in shared memory once per batch;
+//                   serves prompts and single tokens alike, with the same arithmetic in the same order
 //   ssd_gate_norm   y · (z·sigmoid(z)), RMS norm in equal groups, weight, a factor; rounded to the activation dtype
 #include "common.cuh"
 
 namespace {
-constexpr int CONV_RUN = 64;
+constexpr int CONV_RUN = 16;
 constexpr int CONV_MAX_TAPS = 16;
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
@@ -43,20 +45,29 @@ ssd_conv_kernel(const float* __restrict__ proj, int ld, int x_off, const float* 
     if (i0 >= n) return;
     const int i1 = min(n, i0 + CONV_RUN);
     const float* kept = state + ((size_t)slot * 2 + (seq_pos0[s] & 1)) * state_row + conv_off;   // [taps − 1][channels]
-    float wt[CONV_MAX_TAPS];
+    // the taps and the last taps − 1 inputs in registers: every input of the run is read once
+    float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
-    const float b = bias[c];
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+        win[j] = 0.f;
+        if (j < taps - 1) {
+            const int ii = i0 - (taps - 1) + j;
+            win[j] = ii >= 0 ? proj[(size_t)(start + ii) * ld + x_off + c] : kept[(size_t)(taps - 1 + ii) * channels + c];
+        }
+    }
+    const float b = bias[c], w_cur = w[(size_t)c * taps + taps - 1];
     for (int i = i0; i < i1; ++i) {
+        const float cur = proj[(size_t)(start + i) * ld + x_off + c];
         float acc = b;
 #pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-            if (j < taps) {
-                const int ii = i - (taps - 1) + j;
-                const float v = ii >= 0 ? proj[(size_t)(start + ii) * ld + x_off + c] : kept[(size_t)(taps - 1 + ii) * channels + c];
-                acc = fmaf(wt[j], v, acc);
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+            if (j < taps - 1) {
+                acc = fmaf(wt[j], win[j], acc);
+                win[j] = (j + 1 < taps - 1) ? win[j + 1] : cur;
             }
         }
+        acc = fmaf(w_cur, cur, acc);
         out[(size_t)(start + i) * channels + c] = silu_f(acc);
     }
 }
@@ -87,61 +98,146 @@ ssd_conv_state_kernel(const float* __restrict__ proj, int ld, int x_off, float* 
         if (k < taps - 1) next[(size_t)k * channels + c] = v[k];
 }
 
-// R: rows of the state a thread holds.  blockDim = P · NS; thread (p = tid % P, j = tid / P).
-template <int R>
-__global__ void __launch_bounds__(256)
+// NR: rows of the state a warp holds (one column a lane).  A CTA is (head, block of 32 columns, sequence); its warps
+// are the slices of NR rows.  The columns of a state never meet, so nothing but the C-weighted sums over the slices
+// crosses warps: those go through shared memory once per batch of up to 16 tokens.
+constexpr int SC_MAX_BATCH = 16;
+
+__device__ __forceinline__ void sc_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sc_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int NR, bool VEC>
+__global__ void __launch_bounds__(512)
 ssd_scan_kernel(const float* __restrict__ xbc, int channels, const float* __restrict__ proj, int ld, int dt_off,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ Dv,
                 float* __restrict__ state, int state_row, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
-                const int* __restrict__ seq_pos0, float* __restrict__ y, int Hs, int G, int N, int P, int NS) {
+                const int* __restrict__ seq_pos0, float* __restrict__ y, int Hs, int G, int N, int P, int PB, int SC_BATCH) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float red[];          // [2][NS][P]
-    const int h = blockIdx.x, s = blockIdx.y;
+    // shared memory: the C-weighted sums of the slices [2][SC_BATCH][slices][32], then per stage the batch's inputs:
+    // x [SC_BATCH][32], B [SC_BATCH][NP], C [SC_BATCH][NP] (NP: N rounded up to a multiple of 4; SC_BATCH: tokens a
+    // batch, at most 16, fewer where no sequence brings as many)
+    extern __shared__ __align__(16) float sc_sm[];
+    const int h = blockIdx.x / PB, pb = blockIdx.x - h * PB, s = blockIdx.y;
     const int slot = seq_slot[s];
     if (slot < 0) return;
     const int start = seq_start[s], n = seq_start[s + 1] - start, pos0 = seq_pos0[s];
-    const int p = threadIdx.x % P, j = threadIdx.x / P;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, slices = blockDim.x >> 5;
+    const int NP = (N + 3) & ~3, stage_floats = SC_BATCH * (32 + 2 * NP);
+    float* part_sm = sc_sm;
+    float* in_sm = sc_sm + 2 * SC_BATCH * slices * 32;
+    const int p = pb * 32 + lane, n0 = warp * NR;
+    const bool col = p < P;
     const int inner = Hs * P, g = h / (Hs / G);
     const float* S_in = state + ((size_t)slot * 2 + (pos0 & 1)) * state_row + (size_t)h * N * P;
     float* S_out = state + ((size_t)slot * 2 + ((pos0 + n) & 1)) * state_row + (size_t)h * N * P;
-    float S[R];
+    float S[NR];
 #pragma unroll
-    for (int k = 0; k < R; ++k) {
-        const int r = j + k * NS;
-        S[k] = r < N ? S_in[(size_t)r * P + p] : 0.f;
-    }
+    for (int k = 0; k < NR; ++k) S[k] = (col && n0 + k < N) ? S_in[(size_t)(n0 + k) * P + p] : 0.f;
     const float a = -expf(a_log[h]), dtb = dt_bias[h], dh = Dv[h];
-    const int b_off = inner + g * N, c_off = inner + G * N + g * N;
-    for (int i = 0; i < n; ++i) {
-        const size_t row = (size_t)(start + i);
-        const float* xr = xbc + row * channels;
-        const float dt = softplus_f(proj[row * ld + dt_off + h] + dtb);
-        const float decay = expf(a * dt);
-        const float xv = xr[h * P + p];
-        const float dx = dt * xv;
-        float part = 0.f;
-#pragma unroll
-        for (int k = 0; k < R; ++k) {
-            const int r = j + k * NS;
-            if (r < N) {
-                S[k] = fmaf(decay, S[k], xr[b_off + r] * dx);
-                part = fmaf(S[k], xr[c_off + r], part);
+    const int b_col = inner + g * N, c_col = inner + G * N + g * N, x_col = h * P + pb * 32;
+    const int n_x = min(32, P - pb * 32);
+
+    auto fetch = [&](int i0, int stage) {       // all threads: the inputs of the batch that begins at token i0
+        const int nb = min(SC_BATCH, n - i0);
+        float* xs = in_sm + stage * stage_floats;
+        float* bs = xs + SC_BATCH * 32;
+        float* cs = bs + SC_BATCH * NP;
+        for (int idx = threadIdx.x; idx < nb * 32; idx += blockDim.x) {
+            const int ii = idx >> 5, l = idx & 31;
+            if (l < n_x) sc_cp4(xs + idx, xbc + (size_t)(start + i0 + ii) * channels + x_col + l);
+            else xs[idx] = 0.f;
+        }
+        if (VEC) {
+            const int q = N / 4;
+            for (int idx = threadIdx.x; idx < nb * q; idx += blockDim.x) {
+                const int ii = idx / q, c4 = (idx - ii * q) * 4;
+                const float* row = xbc + (size_t)(start + i0 + ii) * channels;
+                sc_cp16(bs + ii * NP + c4, row + b_col + c4);
+                sc_cp16(cs + ii * NP + c4, row + c_col + c4);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < nb * N; idx += blockDim.x) {
+                const int ii = idx / N, c = idx - ii * N;
+                const float* row = xbc + (size_t)(start + i0 + ii) * channels;
+                sc_cp4(bs + ii * NP + c, row + b_col + c);
+                sc_cp4(cs + ii * NP + c, row + c_col + c);
             }
         }
-        float* buf = red + (size_t)(i & 1) * NS * P;
-        buf[j * P + p] = part;
-        __syncthreads();
-        if (j == 0) {
-            float sum = 0.f;
-            for (int q = 0; q < NS; ++q) sum += buf[q * P + p];
-            y[row * inner + h * P + p] = fmaf(dh, xv, sum);
-        }
-    }
+    };
+    fetch(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float dt_raw = lane < min(SC_BATCH, n) ? proj[(size_t)(start + lane) * ld + dt_off + h] : 0.f;
+    for (int i0 = 0, b = 0; i0 < n; i0 += SC_BATCH, ++b) {
+        const int nb = min(SC_BATCH, n - i0), buf = b & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                        // the batch's inputs lie in shared memory, and nobody reads the other stage any more
+        if (i0 + SC_BATCH < n) fetch(i0 + SC_BATCH, buf ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // lane ii works out the step size and the decay of the batch's token ii, and asks for the next batch's number
+        const float dt_mine = softplus_f(dt_raw + dtb), decay_mine = expf(a * dt_mine);
+        const int nxt = i0 + SC_BATCH + lane;
+        dt_raw = nxt < n ? proj[(size_t)(start + nxt) * ld + dt_off + h] : 0.f;
+        const float* xs = in_sm + buf * stage_floats;
+        const float* xp = xs + lane;
+        const float* bs = xs + SC_BATCH * 32 + n0;
+        const float* cs = bs + SC_BATCH * NP;
+        float* mine = part_sm + ((size_t)buf * SC_BATCH * slices + warp) * 32 + lane;
+        const int mine_step = slices * 32;
+        const bool whole = n0 + NR <= N;        // (a slice that ends behind the state's last row checks every row)
+#pragma unroll 2
+        for (int ii = 0; ii < nb; ++ii, xp += 32, bs += NP, cs += NP, mine += mine_step) {
+            const float dt = __shfl_sync(0xffffffffu, dt_mine, ii), decay = __shfl_sync(0xffffffffu, decay_mine, ii);
+            const float dx = dt * xp[0];
+            float part0 = 0.f, part1 = 0.f;
+            if (VEC && whole) {
 #pragma unroll
-    for (int k = 0; k < R; ++k) {
-        const int r = j + k * NS;
-        if (r < N) S_out[(size_t)r * P + p] = S[k];
+                for (int k = 0; k < NR; k += 4) {
+                    const float4 bv = *reinterpret_cast<const float4*>(bs + k), cv = *reinterpret_cast<const float4*>(cs + k);
+                    S[k] = fmaf(decay, S[k], bv.x * dx);         part0 = fmaf(S[k], cv.x, part0);
+                    S[k + 1] = fmaf(decay, S[k + 1], bv.y * dx); part1 = fmaf(S[k + 1], cv.y, part1);
+                    S[k + 2] = fmaf(decay, S[k + 2], bv.z * dx); part0 = fmaf(S[k + 2], cv.z, part0);
+                    S[k + 3] = fmaf(decay, S[k + 3], bv.w * dx); part1 = fmaf(S[k + 3], cv.w, part1);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < NR; ++k) {
+                    if (n0 + k < N) {
+                        S[k] = fmaf(decay, S[k], bs[k] * dx);
+                        part0 = fmaf(S[k], cs[k], part0);
+                    }
+                }
+            }
+            mine[0] = part0 + part1;
+        }
+        __syncthreads();                        // the slices' sums of this batch are complete
+        for (int idx = threadIdx.x; idx < nb * 32; idx += blockDim.x) {
+            const int ii = idx >> 5, l = idx & 31;
+            if (l < n_x) {
+                const float* q = part_sm + ((size_t)buf * SC_BATCH + ii) * slices * 32 + l;
+                float sum = 0.f;
+                for (int w = 0; w < slices; ++w) sum += q[w * 32];
+                y[(size_t)(start + i0 + ii) * inner + x_col + l] = fmaf(dh, xs[idx], sum);
+            }
+        }
+        // (the next pass writes the other buffers only behind its first barrier, which this pass's readers reach first)
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int k = 0; k < NR; ++k)
+        if (col && n0 + k < N) S_out[(size_t)(n0 + k) * P + p] = S[k];
+}
+
+// (asked of the driver once per instantiation and size: more than 48 KB of shared memory is opt-in)
+template <int R, bool V> void scan_allow_smem(size_t smem) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(ssd_scan_kernel<R, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
     }
 }
 
@@ -193,26 +289,33 @@ extern "C" int vlrf_ssd_conv(const float* proj, int ld, int x_off, const float* 
 
 extern "C" int vlrf_ssd_scan(const float* xbc, int channels, const float* proj, int ld, int dt_off, const float* dt_bias,
                              const float* a_log, const float* D, float* state, int state_row, const int* seq_slot,
-                             const int* seq_start, const int* seq_pos0, float* y, int n_seqs, int Hs, int G, int N, int P,
+                             const int* seq_start, const int* seq_pos0, float* y, int n_seqs, int max_new, int Hs, int G, int N, int P,
                              cudaStream_t stream) {
     VLRF_REQUIRE(n_seqs >= 0 && Hs > 0 && G > 0 && N > 0 && P > 0, "ssd_scan: bad sizes");
     VLRF_REQUIRE(Hs % G == 0, "ssd_scan: %d heads cannot share %d groups", Hs, G);
-    VLRF_REQUIRE(P <= 256, "ssd_scan: a head's value size of %d is above 256", P);
+    VLRF_REQUIRE(N <= 512, "ssd_scan: a state of %d rows is above 512", N);
     VLRF_REQUIRE(channels == Hs * P + 2 * G * N && dt_off + Hs <= ld && (size_t)Hs * N * P <= (size_t)state_row,
                  "ssd_scan: the rows do not hold what the sizes say");
     if (n_seqs == 0) return VLRF_OK;
-    const int NS = 256 / P > 0 ? (256 / P < N ? 256 / P : N) : 1;
-    const int rows = (N + NS - 1) / NS;
-    VLRF_REQUIRE(rows <= 128, "ssd_scan: a state of %d rows by %d columns is larger than a CTA's registers hold", N, P);
-    const dim3 grid(Hs, n_seqs), block(P * NS);
-    const size_t smem = (size_t)2 * NS * P * sizeof(float);
-#define GO(R) launch_chained(ssd_scan_kernel<R>, grid, block, smem, stream, xbc, channels, proj, ld, dt_off, dt_bias, a_log, D, state, \
-                             state_row, seq_slot, seq_start, seq_pos0, y, Hs, G, N, P, NS)
-    if (rows <= 8) GO(8);
-    else if (rows <= 16) GO(16);
-    else if (rows <= 32) GO(32);
-    else if (rows <= 64) GO(64);
-    else GO(128);
+    // rows a warp: 8 up to 128 rows (many warps hide the latency of a step that has few CTAs), 16 where the step has
+    // CTAs enough (a decode step of many sequences, bound by reading and writing the states), more for larger states
+    const int PBs = (P + 31) / 32;
+    int sms = 0, devi = 0;
+    cudaGetDevice(&devi);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devi);
+    const bool many = (long long)Hs * PBs * n_seqs >= 4LL * sms;        // enough CTAs to fill the GPU without many warps each
+    const int NR = N > 256 ? 32 : (N > 128 || (many && N >= 64)) ? 16 : N >= 32 ? 8 : 4;
+    const int slices = (N + NR - 1) / NR, PB = (P + 31) / 32;
+    const bool vec = N % 4 == 0 && (Hs * P) % 4 == 0 && channels % 4 == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
+    const dim3 grid(Hs * PB, n_seqs), block(slices * 32);
+    const int batch = max_new < 1 ? 1 : max_new < SC_MAX_BATCH ? max_new : SC_MAX_BATCH;
+    const size_t smem = (size_t)(2 * batch * slices * 32 + 2 * batch * (32 + 2 * ((N + 3) & ~3))) * sizeof(float);
+#define GO(R, V) scan_allow_smem<R, V>(smem); launch_chained(ssd_scan_kernel<R, V>, grid, block, smem, stream, xbc, channels, proj, ld, dt_off, dt_bias, a_log, D, state, \
+                                state_row, seq_slot, seq_start, seq_pos0, y, Hs, G, N, P, PB, batch)
+    if (NR == 4) { if (vec) { GO(4, true); } else { GO(4, false); } }
+    else if (NR == 8) { if (vec) { GO(8, true); } else { GO(8, false); } }
+    else if (NR == 16) { if (vec) { GO(16, true); } else { GO(16, false); } }
+    else { if (vec) { GO(32, true); } else { GO(32, false); } }
 #undef GO
     return vlrf_check_launch("ssd_scan");
 }

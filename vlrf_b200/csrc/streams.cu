@@ -8,6 +8,8 @@
 // With a = null every coefficient is 1 (the sum of the streams: what the model's last norm reads), and `rows` gathers
 // the tokens whose logits are wanted.  S = 1 with a = null is the plain RMS norm of a row.
 //
+// A write that is followed by the next sublayer's read is one kernel (write_read): one pass over the streams.
+//
 // embed_streams: x[t][s] = table[token[t]] · scale for every stream s (scale 1 and one stream: a plain lookup).
 // softcap: v ← cap · tanh(v / cap) over float32 rows (logits).
 #include "common.cuh"
@@ -99,6 +101,57 @@ streams_write_kernel(float* __restrict__ x, const float* __restrict__ mix, const
     }
 }
 
+// The write of one sublayer and the read of the next in one pass over the streams: x' as in the write kernel, then
+// h = RMSnorm(Σ_j a[j] · x'[j]) · w.  The row's u stays in shared memory between the two.
+template <int SMAX, typename OT>
+__global__ void __launch_bounds__(ST_THREADS)
+streams_write_read_kernel(float* __restrict__ x, const float* __restrict__ mix, const float* __restrict__ b,
+                          const float* __restrict__ y, const float* __restrict__ a, const float* __restrict__ w,
+                          OT* __restrict__ out, int d, int S, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float u_sm[];          // [d]
+    __shared__ float m_sm[ST_MAX_STREAMS * ST_MAX_STREAMS];
+    __shared__ float b_sm[ST_MAX_STREAMS], a_sm[ST_MAX_STREAMS];
+    __shared__ float red[ST_THREADS / 32];
+    for (int i = threadIdx.x; i < S * S; i += ST_THREADS) m_sm[i] = mix[i];
+    if (threadIdx.x < S) { b_sm[threadIdx.x] = b[threadIdx.x]; a_sm[threadIdx.x] = a[threadIdx.x]; }
+    __syncthreads();
+    const int t = blockIdx.x;
+    float* xr = x + (size_t)t * S * d;
+    const float* yr = y + (size_t)t * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += ST_THREADS) {
+        float old[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) old[s] = s < S ? xr[(size_t)s * d + i] : 0.f;
+        const float yv = yr[i];
+        float u = 0.f;
+#pragma unroll
+        for (int j = 0; j < SMAX; ++j) {
+            if (j < S) {
+                float v = b_sm[j] * yv;
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s)
+                    if (s < S) v = fmaf(m_sm[s * S + j], old[s], v);
+                xr[(size_t)j * d + i] = v;
+                u = fmaf(a_sm[j], v, u);
+            }
+        }
+        u_sm[i] = u;
+        ss = fmaf(u, u, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < ST_THREADS / 32; ++i) total += red[i];
+    const float inv = 1.f / sqrtf(total / (float)d + eps);
+    OT* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += ST_THREADS) ElemIO<OT>::store(o + i, u_sm[i] * inv * w[i]);
+}
+
 __global__ void softcap_kernel(float* __restrict__ v, long long n, float cap) {
     pdl_wait();
     pdl_launch_dependents();
@@ -152,6 +205,23 @@ extern "C" int vlrf_streams_write(float* x, const float* mix, const float* b, co
     else if (S <= 8) launch_chained(streams_write_kernel<8>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, x, mix, b, y, d, S);
     else launch_chained(streams_write_kernel<16>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, x, mix, b, y, d, S);
     return vlrf_check_launch("streams_write");
+}
+
+extern "C" int vlrf_streams_write_read(float* x, const float* mix, const float* b, const float* y, const float* a, const float* w,
+                                       void* out, int out_dtype, int T, int d, int S, float eps, cudaStream_t stream) {
+    VLRF_REQUIRE(T >= 0 && d > 0 && S > 0 && S <= ST_MAX_STREAMS, "streams_write_read: bad sizes rows=%d d=%d streams=%d", T, d, S);
+    VLRF_REQUIRE((size_t)d * sizeof(float) <= 160 * 1024, "streams_write_read: a row of %d numbers does not fit shared memory", d);
+    VLRF_REQUIRE(out_dtype == VLRF_F32 || out_dtype == VLRF_BF16, "streams_write_read: unknown output dtype %d", out_dtype);
+    VLRF_REQUIRE(a != nullptr, "streams_write_read: the read needs its coefficients");
+    if (T == 0) return VLRF_OK;
+    const size_t smem = (size_t)d * sizeof(float);
+#define GO(M, OT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(streams_write_read_kernel<M, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_chained(streams_write_read_kernel<M, OT>, dim3(T), dim3(ST_THREADS), smem, stream, x, mix, b, y, a, w, (OT*)out, d, S, eps); } while (0)
+#define GO_S(OT) do { if (S <= 2) GO(2, OT); else if (S <= 4) GO(4, OT); else if (S <= 8) GO(8, OT); else GO(16, OT); } while (0)
+    if (out_dtype == VLRF_F32) GO_S(float); else GO_S(__nv_bfloat16);
+#undef GO_S
+#undef GO
+    return vlrf_check_launch("streams_write_read");
 }
 
 extern "C" int vlrf_softcap(float* v, long long n, float cap, cudaStream_t stream) {

@@ -201,6 +201,10 @@ int vlrf_streams_read_norm(const float* x, const int* rows, const float* a, cons
                            int d, int S, float eps, cudaStream_t stream);
 // x[t][j] ← Σ_s mix[s][j] · x[t][s] + b[j] · y[t] for every j at once; x float32 [T][S][d], y float32 [T][d].
 int vlrf_streams_write(float* x, const float* mix, const float* b, const float* y, int T, int d, int S, cudaStream_t stream);
+// The write above followed by the read of the next sublayer (coefficients a, norm weight w) in one pass: x is rewritten,
+// out[t] = RMSnorm(Σ_j a[j] · x'[t][j]) · w.
+int vlrf_streams_write_read(float* x, const float* mix, const float* b, const float* y, const float* a, const float* w, void* out,
+                            int out_dtype, int T, int d, int S, float eps, cudaStream_t stream);
 // v ← cap · tanh(v / cap) over n float32 numbers.
 int vlrf_softcap(float* v, long long n, float cap, cudaStream_t stream);
 
@@ -239,10 +243,11 @@ int vlrf_ssd_conv(const float* proj, int ld, int x_off, const float* w, const fl
                   int conv_off, const int* seq_slot, const int* seq_start, const int* seq_pos0, float* out, int n_seqs, int max_new,
                   int channels, int taps, cudaStream_t stream);
 // The recurrence over every sequence's new tokens.  xbc float32 [T][channels] = [x: H·P | B: G·N | C: G·N]; the step
-// size is softplus(proj[t][dt_off + h] + dt_bias[h]); y float32 [T][H·P].
+// size is softplus(proj[t][dt_off + h] + dt_bias[h]); y float32 [T][H·P].  max_new: the longest run of new tokens of one
+// sequence (it sizes the batches in which the inputs are staged; 1 for a decode step).
 int vlrf_ssd_scan(const float* xbc, int channels, const float* proj, int ld, int dt_off, const float* dt_bias, const float* a_log,
                   const float* D, float* state, int state_row, const int* seq_slot, const int* seq_start, const int* seq_pos0,
-                  float* y, int n_seqs, int Hs, int G, int N, int P, cudaStream_t stream);
+                  float* y, int n_seqs, int max_new, int Hs, int G, int N, int P, cudaStream_t stream);
 // out[r] = factor · groupnorm(y[r] · silu(proj[r][z_off …])) · w: RMS norm in `groups` equal parts; out of out_dtype
 // with row stride ld_out.
 int vlrf_ssd_gate_norm(const float* y, const float* proj, int ld, int z_off, const float* w, void* out, int out_dtype, int ld_out,

@@ -112,7 +112,8 @@ class HyperConnectionBlock:
         u = Σ_s a_q[s] · x_s,    y = sublayer_q(norm_q(u)),    x_t ← Σ_s M_q[s, t] · x_s + b_q[t] · y   (all t at once).
 
     The read and the norm are one kernel (`norm1`, `norm2`: "stream_rmsnorm" parts holding a_q); the sublayer leaves
-    y in float32 scratch (`accumulate=False`); the write is one kernel.  The feed-forward may be absent."""
+    y in float32 scratch (`accumulate=False`); the write is one kernel, and the mixer's write with the feed-forward's
+    read one.  The feed-forward may be absent."""
 
     leaves_row_stats = False
 
@@ -136,8 +137,15 @@ class HyperConnectionBlock:
         y = ctx.ws.get("block_sublayer_out", T, d, torch.float32)
         self.norm1(x, h, n_rows=T)
         self.mixer.forward(h, y, ctx, view, writes_cache, accumulate=False)
-        ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
-        if self.feed_forward is not None:
-            self.norm2(x, h, n_rows=T)
-            self.feed_forward.forward(h, y, ctx, accumulate=False)
-            ops.streams_write(x, self.streams, self.mix2, self.out2, y, T)
+        if self.feed_forward is None:
+            ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
+            return
+        n2 = self.norm2
+        if getattr(n2, "coefficients", None) is not None and getattr(n2, "streams", 0) == self.streams:
+            # the mixer's write and the feed-forward's read in one pass over the streams
+            ops.streams_write_read(x, self.streams, self.mix1, self.out1, y, n2.coefficients, n2.weight, n2.eps, h, T)
+        else:
+            ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
+            n2(x, h, n_rows=T)
+        self.feed_forward.forward(h, y, ctx, accumulate=False)
+        ops.streams_write(x, self.streams, self.mix2, self.out2, y, T)

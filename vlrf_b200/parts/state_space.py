@@ -71,8 +71,8 @@ class StateSpaceMixer:
         ops.ssd_conv(proj, self.x_off, self.conv_w, self.conv_b, view.state, self.conv_off, ctx.seq_slot, ctx.seq_start, ctx.seq_pos0,
                      xbc, ctx.n_seqs, ctx.max_new)
         y = ws.get("ssd_y", T, self.inner, torch.float32)
-        ops.ssd_scan(xbc, proj, self.dt_off, self.dt_bias, self.a_log, self.d_skip, view.state, ctx.seq_slot, ctx.seq_start,
-                     ctx.seq_pos0, y, ctx.n_seqs, self.n_heads, self.n_groups, self.n_state, self.vdim)
+        ops.ssd_scan_step(xbc, proj, self.dt_off, self.dt_bias, self.a_log, self.d_skip, view.state, ctx, y, self.n_heads,
+                          self.n_groups, self.n_state, self.vdim)
         ops.ssd_gate_norm(y, proj, self.z_off, self.norm_w, self.norm_groups, self.eps, factor, merged, T)
 
     def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, accumulate: bool = True) -> None:
