@@ -57,8 +57,15 @@ ssd_conv_kernel(const float* __restrict__ proj, int ld, int x_off, const float* 
         }
     }
     const float b = bias[c], w_cur = w[(size_t)c * taps + taps - 1];
-    for (int i = i0; i < i1; ++i) {
-        const float cur = proj[(size_t)(start + i) * ld + x_off + c];
+    // the run's inputs are asked for together, ahead of the sums that use them one after another
+    float in[CONV_RUN];
+#pragma unroll
+    for (int k = 0; k < CONV_RUN; ++k) in[k] = (i0 + k < i1) ? proj[(size_t)(start + i0 + k) * ld + x_off + c] : 0.f;
+#pragma unroll
+    for (int k = 0; k < CONV_RUN; ++k) {
+        const int i = i0 + k;
+        if (i >= i1) break;
+        const float cur = in[k];
         float acc = b;
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
@@ -189,30 +196,52 @@ ssd_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
         float* mine = part_sm + ((size_t)buf * SC_BATCH * slices + warp) * 32 + lane;
         const int mine_step = slices * 32;
         const bool whole = n0 + NR <= N;        // (a slice that ends behind the state's last row checks every row)
-#pragma unroll 2
-        for (int ii = 0; ii < nb; ++ii, xp += 32, bs += NP, cs += NP, mine += mine_step) {
-            const float dt = __shfl_sync(0xffffffffu, dt_mine, ii), decay = __shfl_sync(0xffffffffu, decay_mine, ii);
-            const float dx = dt * xp[0];
-            float part0 = 0.f, part1 = 0.f;
-            if (VEC && whole) {
+        if (VEC && whole && nb == SC_MAX_BATCH) {
+            // the common case of a prompt, written out for all 16 tokens of a batch: nothing but the loads from shared
+            // memory, the two exchanges of step size and decay, and the multiply-adds
+#pragma unroll
+            for (int ii = 0; ii < SC_MAX_BATCH; ++ii) {
+                const float dt = __shfl_sync(0xffffffffu, dt_mine, ii), decay = __shfl_sync(0xffffffffu, decay_mine, ii);
+                const float dx = dt * xp[ii * 32];
+                const float* bq = bs + ii * NP;
+                const float* cq = cs + ii * NP;
+                float part0 = 0.f, part1 = 0.f;
 #pragma unroll
                 for (int k = 0; k < NR; k += 4) {
-                    const float4 bv = *reinterpret_cast<const float4*>(bs + k), cv = *reinterpret_cast<const float4*>(cs + k);
+                    const float4 bv = *reinterpret_cast<const float4*>(bq + k), cv = *reinterpret_cast<const float4*>(cq + k);
                     S[k] = fmaf(decay, S[k], bv.x * dx);         part0 = fmaf(S[k], cv.x, part0);
                     S[k + 1] = fmaf(decay, S[k + 1], bv.y * dx); part1 = fmaf(S[k + 1], cv.y, part1);
                     S[k + 2] = fmaf(decay, S[k + 2], bv.z * dx); part0 = fmaf(S[k + 2], cv.z, part0);
                     S[k + 3] = fmaf(decay, S[k + 3], bv.w * dx); part1 = fmaf(S[k + 3], cv.w, part1);
                 }
-            } else {
+                mine[ii * mine_step] = part0 + part1;
+            }
+        } else {
+#pragma unroll 2
+            for (int ii = 0; ii < nb; ++ii, xp += 32, bs += NP, cs += NP, mine += mine_step) {
+                const float dt = __shfl_sync(0xffffffffu, dt_mine, ii), decay = __shfl_sync(0xffffffffu, decay_mine, ii);
+                const float dx = dt * xp[0];
+                float part0 = 0.f, part1 = 0.f;
+                if (VEC && whole) {
 #pragma unroll
-                for (int k = 0; k < NR; ++k) {
-                    if (n0 + k < N) {
-                        S[k] = fmaf(decay, S[k], bs[k] * dx);
-                        part0 = fmaf(S[k], cs[k], part0);
+                    for (int k = 0; k < NR; k += 4) {
+                        const float4 bv = *reinterpret_cast<const float4*>(bs + k), cv = *reinterpret_cast<const float4*>(cs + k);
+                        S[k] = fmaf(decay, S[k], bv.x * dx);         part0 = fmaf(S[k], cv.x, part0);
+                        S[k + 1] = fmaf(decay, S[k + 1], bv.y * dx); part1 = fmaf(S[k + 1], cv.y, part1);
+                        S[k + 2] = fmaf(decay, S[k + 2], bv.z * dx); part0 = fmaf(S[k + 2], cv.z, part0);
+                        S[k + 3] = fmaf(decay, S[k + 3], bv.w * dx); part1 = fmaf(S[k + 3], cv.w, part1);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NR; ++k) {
+                        if (n0 + k < N) {
+                            S[k] = fmaf(decay, S[k], bs[k] * dx);
+                            part0 = fmaf(S[k], cs[k], part0);
+                        }
                     }
                 }
+                mine[0] = part0 + part1;
             }
-            mine[0] = part0 + part1;
         }
         __syncthreads();                        // the slices' sums of this batch are complete
         for (int idx = threadIdx.x; idx < nb * 32; idx += blockDim.x) {
