@@ -963,7 +963,7 @@ def ssd_gate_norm(y, proj, z_off: int, weight, groups: int, eps: float, factor: 
 
 #: largest head size of the attention with key and value sizes of their own; most taps and largest value size of the
 #: state-space kernels
-WINDOW_HEAD_MAX, SSD_MAX_TAPS, SSD_MAX_VDIM = 256, 16, 256
+WINDOW_HEAD_MAX, SSD_MAX_TAPS, SSD_MAX_VDIM, SSD_MAX_STATE = 256, 16, 4096, 512
 
 
 #: bfloat16 attention with key and value sizes of their own on the tensor cores where the kernel takes the sizes (off: the

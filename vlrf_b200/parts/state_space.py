@@ -44,8 +44,9 @@ class StateSpaceMixer:
             raise ValueError("state-space mixer: dt_bias, A_log and D have one number per head")
         if norm_w.shape[0] != inner or norm_groups < 1 or inner % norm_groups != 0 or w_out.shape[1] != inner:
             raise ValueError("state-space mixer: the norm and the output projection take the heads' merged values")
-        if P > ops.SSD_MAX_VDIM:
-            raise ValueError(f"state-space mixer: a head's value size of {P} is above the {ops.SSD_MAX_VDIM} the kernels take")
+        if P > ops.SSD_MAX_VDIM or N > ops.SSD_MAX_STATE:
+            raise ValueError(f"state-space mixer: a state of {N} rows by {P} columns is above the {ops.SSD_MAX_STATE} by "
+                             f"{ops.SSD_MAX_VDIM} the kernels take")
         self.n_heads, self.vdim, self.n_state, self.n_groups = Hs, P, N, G
         self.norm_groups, self.eps = int(norm_groups), float(eps)
         self.inner, self.channels, self.taps = inner, channels, int(conv_w.shape[1])
