@@ -31,20 +31,18 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int slot = tok_slot[t];
-    if (slot < 0) return;  // padding row
+    if (slot < 0) return;  // padding row (the whole CTA leaves: no barrier is missed)
     const int pos = tok_pos[t];
     const float* row = proj + (size_t)t * ld;
     const int half = rot / 2;
-    const float p = (float)pos;
+    // the token's cosines and sines once, for all heads: [half] each
+    extern __shared__ float cs_sm[];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freq[i], &cs_sm[half + i], &cs_sm[i]);
+    __syncthreads();
     auto rotated = [&](const float* head, int c) -> float {
         if (c >= rot) return head[c];
-        float s, co;
-        if (c < half) {
-            sincosf(p * freq[c], &s, &co);
-            return head[c] * co - head[c + half] * s;
-        }
-        sincosf(p * freq[c - half], &s, &co);
-        return head[c] * co + head[c - half] * s;
+        if (c < half) return head[c] * cs_sm[c] - head[c + half] * cs_sm[half + c];
+        return head[c] * cs_sm[c - half] + head[c - half] * cs_sm[c];
     };
     for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
         const int h = i / dk, c = i - h * dk;
@@ -152,11 +150,11 @@ extern "C" int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_
     VLRF_REQUIRE(dev_err != nullptr, "qkv_rope_append: needs the device error word");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        launch_chained(qkv_rope_append_kernel<float>, dim3(T), dim3(128), (size_t)0, stream, proj, ld, q_off, k_off, v_off, freq, rot,
+        launch_chained(qkv_rope_append_kernel<float>, dim3(T), dim3(128), (size_t)rot * sizeof(float), stream, proj, ld, q_off, k_off, v_off, freq, rot,
                        (float*)q_out, ldq, (float*)Kc, (float*)Vc, block_table, max_blocks, tok_slot, tok_pos, H, Hkv, dk, dv, BT,
                        write_cache, dev_err);
     else if (dtype == VLRF_BF16)
-        launch_chained(qkv_rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)0, stream, proj, ld, q_off, k_off, v_off, freq,
+        launch_chained(qkv_rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)rot * sizeof(float), stream, proj, ld, q_off, k_off, v_off, freq,
                        rot, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)Kc, (__nv_bfloat16*)Vc, block_table, max_blocks, tok_slot,
                        tok_pos, H, Hkv, dk, dv, BT, write_cache, dev_err);
     else

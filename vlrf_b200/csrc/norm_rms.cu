@@ -85,6 +85,20 @@ __global__ void gate_mul_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __
     *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// float32 gate and value, bfloat16 result, four a thread (rows and columns on 16-byte boundaries)
+__global__ void gate_mul_f32x4_kernel(const float* a, int lda, const float* b, int ldb, __nv_bfloat16* out, int ldo, int rows, int cols4,
+                                      int act) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols4) return;
+    const int r = (int)(i / cols4), c = (int)(i - (long long)r * cols4) * 4;
+    const float4 g = *reinterpret_cast<const float4*>(a + (size_t)r * lda + c), v = *reinterpret_cast<const float4*>(b + (size_t)r * ldb + c);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(gate_f(act, g.x) * v.x, gate_f(act, g.y) * v.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(gate_f(act, g.z) * v.z, gate_f(act, g.w) * v.w);
+    *reinterpret_cast<uint2*>(out + (size_t)r * ldo + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 template <typename AT, typename BT, typename OT>
 __global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, int act) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
@@ -145,6 +159,9 @@ extern "C" int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b,
     else if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(bf, bf, bf);
     else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_F32) GO(float, float, float);
     else if (a_dtype == VLRF_F32 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(float, bf, bf);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_BF16 && aligned && lda % 4 == 0 && ldb % 4 == 0)
+        launch_chained(gate_mul_f32x4_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), (size_t)0, stream, (const float*)a, lda,
+                       (const float*)b, ldb, (bf*)out, ldo, rows, cols / 4, act);
     else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_BF16) GO(float, float, bf);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul: dtypes %d, %d -> %d are not taken", a_dtype, b_dtype, out_dtype);
 #undef GO
