@@ -58,13 +58,14 @@ def make_engine(kot_dirs, name, dtype, max_tokens):
     return eng
 
 
-def compare(got, want, dtype, what, model):
+def compare(got, want, dtype, what, model, tol=None):
+    tol = TOL[dtype] if tol is None else tol
     worst = 0.0
     for i, (g, t) in enumerate(zip(got, want)):
         assert g.shape == t.shape, f"{what}: request {i} has shape {tuple(g.shape)}, expected {tuple(t.shape)}"
         assert torch.isfinite(g).all(), f"{what}: request {i} has non-finite logits (something unwritten was read)"
         err = (g.double() - t).abs().max(dim=1).values / float(t.abs().max())
-        bad = (err > TOL[dtype]).nonzero()
+        bad = (err > tol).nonzero()
         assert bad.numel() == 0, (f"{what} ({model}, {dtype}): request {i} (length {len(t)}) first differs at position "
                                   f"{int(bad[0])} with error {float(err[bad[0]]):.3e} of the logit scale")
         worst = max(worst, float(err.max()))
