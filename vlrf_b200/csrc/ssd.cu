@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(128)
 ssd_conv_kernel(const float* __restrict__ proj, int ld, int x_off, const float* __restrict__ w, const float* __restrict__ bias,
                 const float* __restrict__ state, int state_row, int conv_off, const int* __restrict__ seq_slot,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, float* __restrict__ out, int channels,
-                int taps) {
+                int taps, float* __restrict__ keep) {
     pdl_wait();
     pdl_launch_dependents();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -76,6 +76,14 @@ ssd_conv_kernel(const float* __restrict__ proj, int ld, int x_off, const float* 
         }
         acc = fmaf(w_cur, cur, acc);
         out[(size_t)(start + i) * channels + c] = silu_f(acc);
+    }
+    // keep != null (every sequence is one run: this thread alone has read the channel's kept inputs): the last taps − 1
+    // inputs into the copy that the step writes, which may be the copy it read
+    if (keep != nullptr) {
+        float* next = keep + ((size_t)slot * 2 + ((seq_pos0[s] + n) & 1)) * state_row + conv_off;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < taps - 1) next[(size_t)j * channels + c] = win[j];
     }
 }
 
@@ -305,10 +313,11 @@ extern "C" int vlrf_ssd_conv(const float* proj, int ld, int x_off, const float* 
     VLRF_REQUIRE(x_off + channels <= ld && conv_off + (taps - 1) * channels <= state_row, "ssd_conv: columns lie outside the row");
     if (n_seqs == 0 || max_new == 0) return VLRF_OK;
     const dim3 grid((channels + 127) / 128, n_seqs, (max_new + CONV_RUN - 1) / CONV_RUN);
+    const bool one_run = max_new <= CONV_RUN;       // then the convolution's threads leave the kept inputs themselves
     launch_chained(ssd_conv_kernel, grid, dim3(128), (size_t)0, stream, proj, ld, x_off, w, bias, (const float*)state, state_row,
-                   conv_off, seq_slot, seq_start, seq_pos0, out, channels, taps);
+                   conv_off, seq_slot, seq_start, seq_pos0, out, channels, taps, (one_run && taps > 1) ? state : (float*)nullptr);
     if (vlrf_check_launch("ssd_conv") != VLRF_OK) return VLRF_ERR_CUDA;
-    if (taps > 1) {
+    if (taps > 1 && !one_run) {
         launch_chained(ssd_conv_state_kernel, dim3((channels + 127) / 128, n_seqs), dim3(128), (size_t)0, stream, proj, ld, x_off,
                        state, state_row, conv_off, seq_slot, seq_start, seq_pos0, channels, taps);
         return vlrf_check_launch("ssd_conv_state");

@@ -131,12 +131,14 @@ class DecoderModel:
         x = ctx.ws.get("residual", ctx.n_tokens, self.residual_width, torch.float32)
         ctx.ws.row_stats.forget()                      # nothing is known about the rows of the step before
         ctx.ws.input_cast = None
+        ctx.ws.normed_ready = None
         self.embedding(ctx, x)
         if not getattr(self.embedding, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
         for i, call in enumerate(self.schedule):
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
+            ctx.next_block = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
             if not getattr(self.layers[call.layer], "leaves_row_stats", False):
                 ctx.ws.row_stats.forget()              # a block of another kind that does not vouch for them

@@ -112,8 +112,9 @@ class HyperConnectionBlock:
         u = Σ_s a_q[s] · x_s,    y = sublayer_q(norm_q(u)),    x_t ← Σ_s M_q[s, t] · x_s + b_q[t] · y   (all t at once).
 
     The read and the norm are one kernel (`norm1`, `norm2`: "stream_rmsnorm" parts holding a_q); the sublayer leaves
-    y in float32 scratch (`accumulate=False`); the write is one kernel, and the mixer's write with the feed-forward's
-    read one.  The feed-forward may be absent."""
+    y in float32 scratch (`accumulate=False`); a write and the read that follows it (the mixer's write and the
+    feed-forward's read; a layer's last write and the next layer's first read, where the model says that a block of this
+    kind runs next) are one kernel.  The feed-forward may be absent."""
 
     leaves_row_stats = False
 
@@ -129,23 +130,40 @@ class HyperConnectionBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+    def _fusable_read(self, norm) -> bool:
+        return getattr(norm, "coefficients", None) is not None and getattr(norm, "streams", 0) == self.streams
+
+    def _write(self, x, mix, out, y, h, ctx: StepContext, reader) -> bool:
+        """A sublayer's write; with `reader` (the norm part of whatever reads the streams next) the read in the same pass.
+        Returns whether h holds that read."""
         from ..csrc import ops
+        T = ctx.n_tokens
+        if reader is not None and self._fusable_read(reader):
+            ops.streams_write_read(x, self.streams, mix, out, y, reader.coefficients, reader.weight, reader.eps, h, T)
+            return True
+        ops.streams_write(x, self.streams, mix, out, y, T)
+        return False
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
         T, d = ctx.n_tokens, x.shape[1] // self.streams
-        ctx.ws.row_stats.forget()
-        h = ctx.ws.get("block_normed", T, d, ctx.act_dtype)
-        y = ctx.ws.get("block_sublayer_out", T, d, torch.float32)
-        self.norm1(x, h, n_rows=T)
+        ws = ctx.ws
+        ws.row_stats.forget()
+        h = ws.get("block_normed", T, d, ctx.act_dtype)
+        y = ws.get("block_sublayer_out", T, d, torch.float32)
+        # the block ahead may have left this block's first read with its last write
+        if ws.normed_ready != (x.data_ptr(), T, id(ctx), id(self.norm1)):
+            self.norm1(x, h, n_rows=T)
+        ws.normed_ready = None
+        # who reads the streams after this block's last write: the next block's first norm, if it is one of this kind
+        nb = getattr(ctx, "next_block", None)
+        after = nb.norm1 if isinstance(nb, HyperConnectionBlock) and nb.streams == self.streams else None
         self.mixer.forward(h, y, ctx, view, writes_cache, accumulate=False)
         if self.feed_forward is None:
-            ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
+            if self._write(x, self.mix1, self.out1, y, h, ctx, after):
+                ws.normed_ready = (x.data_ptr(), T, id(ctx), id(after))
             return
-        n2 = self.norm2
-        if getattr(n2, "coefficients", None) is not None and getattr(n2, "streams", 0) == self.streams:
-            # the mixer's write and the feed-forward's read in one pass over the streams
-            ops.streams_write_read(x, self.streams, self.mix1, self.out1, y, n2.coefficients, n2.weight, n2.eps, h, T)
-        else:
-            ops.streams_write(x, self.streams, self.mix1, self.out1, y, T)
-            n2(x, h, n_rows=T)
+        if not self._write(x, self.mix1, self.out1, y, h, ctx, self.norm2):
+            self.norm2(x, h, n_rows=T)
         self.feed_forward.forward(h, y, ctx, accumulate=False)
-        ops.streams_write(x, self.streams, self.mix2, self.out2, y, T)
+        if self._write(x, self.mix2, self.out2, y, h, ctx, after):
+            ws.normed_ready = (x.data_ptr(), T, id(ctx), id(after))

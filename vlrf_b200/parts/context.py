@@ -30,6 +30,9 @@ class Workspace:
         #: (address, rows, step) of the float32 rows whose rounding to the activation dtype lies in "block_input", or
         #: None: written by blocks whose norm leaves that rounding, forgotten by the model after every other layer
         self.input_cast = None
+        #: (address of the residual rows, rows, step, the norm part) whose read lies in "block_normed" already: a block
+        #: whose last write also made the next block's read says so here; forgotten by the model at every step's start
+        self.normed_ready = None
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, rows, cols, dtype)
@@ -91,3 +94,5 @@ class StepContext:
     host_seq_slots: list = dataclasses.field(default_factory=list)
     host_seq_lens: list = dataclasses.field(default_factory=list)
     host_seq_pos0: list = dataclasses.field(default_factory=list)
+    #: the block that the model runs after the one it is calling (None behind the last): a block may prepare its input
+    next_block: object = None
